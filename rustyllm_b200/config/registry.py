@@ -40,14 +40,15 @@ def known_architectures() -> Sequence[str]:
 
 
 def resolve_architecture(config_dict: Mapping[str, Any]) -> Architecture:
-    """Pick the architecture by ``architectures[0]``, else by ``model_type``."""
+    """Pick the architecture by ``architectures[0]``, else by ``model_type``, else by ``architecture``."""
     candidates = []
     archs = config_dict.get("architectures")
     if isinstance(archs, (list, tuple)):
         candidates.extend(a for a in archs if isinstance(a, str))
-    mt = config_dict.get("model_type")
-    if isinstance(mt, str):
-        candidates.append(mt)
+    for key in ("model_type", "architecture"):      # some designs name themselves under "architecture"
+        mt = config_dict.get(key)
+        if isinstance(mt, str):
+            candidates.append(mt)
     for c in candidates:
         if c in _ARCHITECTURES:
             return _ARCHITECTURES[c]

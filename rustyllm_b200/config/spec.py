@@ -80,6 +80,18 @@ class LayerSpec:
 
 
 @dataclass(frozen=True)
+class Injection:
+    """Something added to the residual stream between layers: before the layer run at place
+    ``before_run`` of the schedule, part ``part`` of ``ModelSpec.inject_parts`` is called with
+    ``args`` (for "pass_entry": the number of the pass and whether the embedding's output is
+    added again)."""
+
+    before_run: int
+    part: int
+    args: Dict[str, Any] = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
 class ModelSpec:
     architecture: str
     vocab_size: int
@@ -93,6 +105,8 @@ class ModelSpec:
     eos_token_id: Tuple[int, ...] = ()
     bos_token_id: Tuple[int, ...] = ()
     ignored_tensors: Tuple[str, ...] = ()  # names that may be in the file and are not read
+    inject_parts: Tuple[PartSpec, ...] = ()      # parts of role "inject" (parts/inject.py)
+    injections: Tuple[Injection, ...] = ()       # where along the schedule they act, in running order
 
     def validate(self) -> None:
         n = len(self.layers)
@@ -103,6 +117,11 @@ class ModelSpec:
         for i in self.schedule:
             if not (0 <= i < n):
                 raise ValueError(f"schedule names layer {i}, but there are {n} layers")
+        for inj in self.injections:
+            if not (0 <= inj.before_run < len(self.schedule)):
+                raise ValueError(f"an injection stands before run {inj.before_run}, but the schedule has {len(self.schedule)} runs")
+            if not (0 <= inj.part < len(self.inject_parts)):
+                raise ValueError(f"an injection names inject part {inj.part}, but there are {len(self.inject_parts)}")
         for li, layer in enumerate(self.layers):
             src = layer.cache_from
             if src is not None:

@@ -29,7 +29,8 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
 attention_simt_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k_pool,
                       const T* __restrict__ v_pool, const int* __restrict__ page_table, int max_pages,
                       const int* __restrict__ slot_of_token, const int* __restrict__ positions,
-                      T* __restrict__ out, int ldo, int H, int G, int hd, int vd, float scale, int window) {
+                      T* __restrict__ out, int ldo, int H, int G, int hd, int vd, float scale, int window,
+                      int sink, const T* __restrict__ gate, int ldg) {
   constexpr int NE = ATT_MAX_HD / 32;
   __shared__ float s_acc[ATT_WARPS][ATT_MAX_HD];
   __shared__ float s_max[ATT_WARPS], s_sum[ATT_WARPS];
@@ -96,10 +97,11 @@ attention_simt_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k_
     if (d < vd) s_acc[warp][d] = acc[e];
   }
   __syncthreads();
-  float M = -INFINITY;
+  // sink: one more term in the denominator with score 0 and no value, p_j = e^{s_j} / (1 + sum e^{s_t})
+  float M = sink ? 0.f : -INFINITY;
 #pragma unroll
   for (int w = 0; w < ATT_WARPS; ++w) M = fmaxf(M, s_max[w]);
-  float wgt[ATT_WARPS], L = 0.f;
+  float wgt[ATT_WARPS], L = sink ? expf(-M) : 0.f;
 #pragma unroll
   for (int w = 0; w < ATT_WARPS; ++w) {
     wgt[w] = s_max[w] > -INFINITY ? expf(s_max[w] - M) : 0.f;
@@ -111,7 +113,9 @@ attention_simt_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k_
     float o = 0.f;
 #pragma unroll
     for (int w = 0; w < ATT_WARPS; ++w) o += s_acc[w][d] * wgt[w];
-    rl_st(orow + d, o * inv);
+    o *= inv;
+    if (gate) o *= 1.0f / (1.0f + expf(-rl_ld(gate + (size_t)m * ldg + (size_t)h * vd + d)));   // output gate, in 32-bit
+    rl_st(orow + d, o);
   }
 }
 
@@ -119,11 +123,16 @@ attention_simt_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k_
 // [h*vd, (h+1)*vd).  k_pool: [num_pages, G, RL_PAGE, hd], v_pool: [num_pages, G, RL_PAGE, vd]
 // (value heads may be narrower or wider than key heads: the reference keeps value_dim apart
 // from head_dim, src/model.rs:33, 67-69), both in the same dtype as q.
-extern "C" int rl_attention_simt(const void* q, int ldq, const void* k_pool, const void* v_pool,
-                                 int dtype, const int* page_table, int max_pages,
-                                 const int* slot_of_token, const int* positions, void* out, int ldo,
-                                 int num_tokens, int num_heads, int num_kv_heads, int head_dim, int value_dim,
-                                 float scale, int window, cudaStream_t stream) {
+//
+// sink != 0: the softmax has one more term in its denominator, of score 0 and without a value.
+// gate (may be null): [M, ldg], same dtype; head h's output is multiplied element by element with
+// sigmoid(gate[m, h*vd + i]) before it is stored.
+extern "C" int rl_attention_simt_gated(const void* q, int ldq, const void* k_pool, const void* v_pool,
+                                       int dtype, const int* page_table, int max_pages,
+                                       const int* slot_of_token, const int* positions, void* out, int ldo,
+                                       int num_tokens, int num_heads, int num_kv_heads, int head_dim, int value_dim,
+                                       float scale, int window, int sink, const void* gate, int ldg, cudaStream_t stream) {
+  RL_REQUIRE(gate == nullptr || ldg >= num_heads * value_dim, "rl_attention_simt: the gate's row stride is too small");
   RL_REQUIRE(num_tokens >= 0 && num_heads > 0 && num_kv_heads > 0, "rl_attention_simt: bad sizes");
   RL_REQUIRE(num_heads % num_kv_heads == 0, "rl_attention_simt: %d heads are no multiple of %d KV heads",
              num_heads, num_kv_heads);
@@ -137,13 +146,24 @@ extern "C" int rl_attention_simt(const void* q, int ldq, const void* k_pool, con
   if (dtype == RL_F32)
     attention_simt_kernel<float><<<grid, ATT_WARPS * 32, 0, stream>>>(
         (const float*)q, ldq, (const float*)k_pool, (const float*)v_pool, page_table, max_pages,
-        slot_of_token, positions, (float*)out, ldo, num_heads, num_kv_heads, head_dim, value_dim, scale, window);
+        slot_of_token, positions, (float*)out, ldo, num_heads, num_kv_heads, head_dim, value_dim, scale, window,
+        sink, (const float*)gate, ldg);
   else if (dtype == RL_BF16)
     attention_simt_kernel<__nv_bfloat16><<<grid, ATT_WARPS * 32, 0, stream>>>(
         (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_table,
-        max_pages, slot_of_token, positions, (__nv_bfloat16*)out, ldo, num_heads, num_kv_heads, head_dim, value_dim, scale, window);
+        max_pages, slot_of_token, positions, (__nv_bfloat16*)out, ldo, num_heads, num_kv_heads, head_dim, value_dim, scale, window,
+        sink, (const __nv_bfloat16*)gate, ldg);
   else
     RL_REQUIRE(false, "rl_attention_simt: unknown dtype %d", dtype);
   RL_LAUNCH_CHECK("rl_attention_simt");
   return RL_OK;
+}
+
+extern "C" int rl_attention_simt(const void* q, int ldq, const void* k_pool, const void* v_pool,
+                                 int dtype, const int* page_table, int max_pages,
+                                 const int* slot_of_token, const int* positions, void* out, int ldo,
+                                 int num_tokens, int num_heads, int num_kv_heads, int head_dim, int value_dim,
+                                 float scale, int window, cudaStream_t stream) {
+  return rl_attention_simt_gated(q, ldq, k_pool, v_pool, dtype, page_table, max_pages, slot_of_token, positions, out, ldo,
+                                 num_tokens, num_heads, num_kv_heads, head_dim, value_dim, scale, window, 0, nullptr, 0, stream);
 }

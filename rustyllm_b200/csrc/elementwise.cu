@@ -260,3 +260,135 @@ extern "C" int rl_convert(const void* in, int in_dtype, void* out, int out_dtype
   RL_LAUNCH_CHECK("rl_convert");
   return RL_OK;
 }
+
+// ------------------------------------------------------------------ embedding with learned positions
+// x[m, :] = E[token_m, :] + P[position_m, :], summed in 32-bit (a learned absolute position
+// table beside the token table; neither is scaled).
+template <typename T>
+__global__ void embedding_pos_kernel(const T* __restrict__ table, const T* __restrict__ pos_table,
+                                     const int* __restrict__ ids, const int* __restrict__ positions,
+                                     float* __restrict__ out, int d, int vocab, int max_pos, int* __restrict__ err) {
+  rl_pdl_trigger();
+  rl_pdl_wait();
+  const int m = blockIdx.x;
+  int id = ids[m], p = positions[m];
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) atomicExch(err, 1);
+    id = 0;
+  }
+  if (p < 0 || p >= max_pos) {     // a position beyond the table: refuse instead of reading outside it
+    if (threadIdx.x == 0) atomicExch(err, 2);
+    p = 0;
+  }
+  const T* row = table + (size_t)id * d;
+  const T* prow = pos_table + (size_t)p * d;
+  float* o = out + (size_t)m * d;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) o[i] = rl_ld(row + i) + rl_ld(prow + i);
+}
+
+extern "C" int rl_embedding_pos(const void* table, const void* pos_table, int table_dtype, const int* ids,
+                                const int* positions, float* out, int num_tokens, int hidden, int vocab,
+                                int max_positions, int* err, cudaStream_t stream) {
+  RL_REQUIRE(num_tokens >= 0 && hidden > 0 && vocab > 0 && max_positions > 0,
+             "rl_embedding_pos: bad sizes M=%d d=%d V=%d P=%d", num_tokens, hidden, vocab, max_positions);
+  RL_REQUIRE(err != nullptr, "rl_embedding_pos: the error flag pointer is null");
+  if (num_tokens == 0) return RL_OK;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (table_dtype == RL_F32)
+    rl_launch_pdl(embedding_pos_kernel<float>, num_tokens, threads, 0, stream, (const float*)table, (const float*)pos_table,
+                  ids, positions, out, hidden, vocab, max_positions, err);
+  else if (table_dtype == RL_BF16)
+    rl_launch_pdl(embedding_pos_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream, (const __nv_bfloat16*)table,
+                  (const __nv_bfloat16*)pos_table, ids, positions, out, hidden, vocab, max_positions, err);
+  else
+    RL_REQUIRE(false, "rl_embedding_pos: unknown table dtype %d", table_dtype);
+  RL_LAUNCH_CHECK("rl_embedding_pos");
+  return RL_OK;
+}
+
+// ------------------------------------------------------------------ additions to the residual between layers
+// x[m, :] += (again ? again[m, :] : 0) + (vec ? vec[:] : 0), all float: what a model adds to the
+// residual stream where a group of layers is entered (a copy of an earlier state of the stream,
+// a learned vector of the pass).  The two are summed first, then added to x.
+template <typename TV>
+__global__ void residual_inject_kernel(float* __restrict__ x, const float* __restrict__ again,
+                                       const TV* __restrict__ vec, size_t total, int d) {
+  rl_pdl_trigger();
+  rl_pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    float a = again ? again[i] : 0.f;
+    if (vec) a += rl_ld(vec + (i % d));
+    x[i] += a;
+  }
+}
+
+extern "C" int rl_residual_inject(float* x, const float* again, const void* vec, int vec_dtype, int num_tokens,
+                                  int hidden, cudaStream_t stream) {
+  RL_REQUIRE(num_tokens >= 0 && hidden > 0, "rl_residual_inject: bad sizes M=%d d=%d", num_tokens, hidden);
+  if (num_tokens == 0 || (again == nullptr && vec == nullptr)) return RL_OK;
+  const size_t total = (size_t)num_tokens * hidden;
+  const int threads = 256;
+  const size_t want = (total + threads - 1) / threads;
+  const int blocks = (int)(want < (size_t)rl_num_sms() * 16 ? want : (size_t)rl_num_sms() * 16);
+  if (vec_dtype == RL_F32)
+    rl_launch_pdl(residual_inject_kernel<float>, blocks, threads, 0, stream, x, again, (const float*)vec, total, hidden);
+  else if (vec_dtype == RL_BF16)
+    rl_launch_pdl(residual_inject_kernel<__nv_bfloat16>, blocks, threads, 0, stream, x, again, (const __nv_bfloat16*)vec, total, hidden);
+  else
+    RL_REQUIRE(false, "rl_residual_inject: unknown dtype %d", vec_dtype);
+  RL_LAUNCH_CHECK("rl_residual_inject");
+  return RL_OK;
+}
+
+// ------------------------------------------------------------------ soft cap of logits
+// y = cap * tanh(y / cap) in place, float.
+__global__ void softcap_kernel(float* __restrict__ y, size_t total, float cap, float inv_cap) {
+  rl_pdl_trigger();
+  rl_pdl_wait();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x)
+    y[i] = cap * tanhf(y[i] * inv_cap);
+}
+
+extern "C" int rl_softcap(float* y, long long n, float cap, cudaStream_t stream) {
+  RL_REQUIRE(n >= 0 && cap > 0.f, "rl_softcap: bad arguments n=%lld cap=%g", n, (double)cap);
+  if (n == 0) return RL_OK;
+  const int threads = 256;
+  const long long want = (n + threads - 1) / threads;
+  const int blocks = (int)(want < rl_num_sms() * 16 ? want : rl_num_sms() * 16);
+  rl_launch_pdl(softcap_kernel, blocks, threads, 0, stream, y, (size_t)n, cap, 1.0f / cap);
+  RL_LAUNCH_CHECK("rl_softcap");
+  return RL_OK;
+}
+
+// ------------------------------------------------------------------ sigmoid gate
+// y[m, i] *= 1 / (1 + exp(-g[m, i])) for i < n; the sigmoid in 32-bit.  g may be a view into a
+// wider buffer (row stride ldg).
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ y, int ldy, const T* __restrict__ g, int ldg, int M, int n) {
+  rl_pdl_trigger();
+  rl_pdl_wait();
+  const size_t total = (size_t)M * n;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t m = idx / n, i = idx % n;
+    const float gate = 1.0f / (1.0f + expf(-rl_ld(g + m * ldg + i)));
+    T* p = y + m * ldy + i;
+    rl_st(p, rl_ld(p) * gate);
+  }
+}
+
+extern "C" int rl_sigmoid_gate(void* y, int ldy, const void* g, int ldg, int dtype, int num_tokens, int n, cudaStream_t stream) {
+  RL_REQUIRE(num_tokens >= 0 && n > 0 && ldy >= n && ldg >= n, "rl_sigmoid_gate: bad sizes M=%d n=%d", num_tokens, n);
+  if (num_tokens == 0) return RL_OK;
+  const size_t total = (size_t)num_tokens * n;
+  const int threads = 256;
+  const size_t want = (total + threads - 1) / threads;
+  const int blocks = (int)(want < (size_t)rl_num_sms() * 16 ? want : (size_t)rl_num_sms() * 16);
+  if (dtype == RL_F32)
+    rl_launch_pdl(sigmoid_gate_kernel<float>, blocks, threads, 0, stream, (float*)y, ldy, (const float*)g, ldg, num_tokens, n);
+  else if (dtype == RL_BF16)
+    rl_launch_pdl(sigmoid_gate_kernel<__nv_bfloat16>, blocks, threads, 0, stream, (__nv_bfloat16*)y, ldy, (const __nv_bfloat16*)g, ldg, num_tokens, n);
+  else
+    RL_REQUIRE(false, "rl_sigmoid_gate: unknown dtype %d", dtype);
+  RL_LAUNCH_CHECK("rl_sigmoid_gate");
+  return RL_OK;
+}

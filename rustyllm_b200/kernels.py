@@ -44,6 +44,18 @@ _SIGNATURES = {
     "rl_attention_simt": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
                           _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
                           _c_void_p],
+    "rl_attention_simt_gated": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
+                                _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
+                                _c_int, _c_void_p, _c_int, _c_void_p],
+    "rl_embedding_pos": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
+                         _c_void_p, _c_void_p],
+    "rl_residual_inject": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "rl_softcap": [_c_void_p, _c_ll, _c_float, _c_void_p],
+    "rl_sigmoid_gate": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "rl_moe_route": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
+                     _c_void_p],
+    "rl_moe_experts": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
+                       _c_int, _c_void_p, _c_void_p, _c_void_p],
     "rl_repeat_penalty": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_float, _c_void_p],
     "rl_argmax": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p],
     "rl_sample_temperature": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
@@ -160,6 +172,92 @@ def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, err_fla
     _count()
 
 
+def embedding_pos(table: torch.Tensor, pos_table: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor,
+                  out: torch.Tensor, err_flag: torch.Tensor) -> None:
+    """out[m, :] = table[ids[m], :] + pos_table[positions[m], :] as float32.  err_flag (int32[1]) is set
+    to 1 on a bad id and to 2 on a position outside ``pos_table``."""
+    _need(table, "table"); _need(pos_table, "pos_table", table.dtype); _need(ids, "ids", torch.int32)
+    _need(positions, "positions", torch.int32); _need(out, "out", torch.float32); _need(err_flag, "err_flag", torch.int32)
+    V, d = table.shape
+    M = ids.numel()
+    assert out.shape == (M, d) and pos_table.shape[1] == d and positions.numel() == M
+    _check(library().rl_embedding_pos(table.data_ptr(), pos_table.data_ptr(), _dt(table), ids.data_ptr(), positions.data_ptr(),
+                                      out.data_ptr(), M, d, V, pos_table.shape[0], err_flag.data_ptr(), _stream()),
+           "rl_embedding_pos")
+    _count()
+
+
+def residual_inject(x: torch.Tensor, again: Optional[torch.Tensor], vec: Optional[torch.Tensor]) -> None:
+    """x[m, :] += again[m, :] + vec[:] (either may be ``None``); x and again float32 [M, d], vec [d]."""
+    _need(x, "x", torch.float32)
+    M, d = x.shape
+    if again is not None:
+        _need(again, "again", torch.float32)
+        assert again.shape == x.shape
+    if vec is not None:
+        _need(vec, "vec")
+        assert vec.numel() == d
+    if again is None and vec is None:
+        return
+    _check(library().rl_residual_inject(x.data_ptr(), _ptr(again), _ptr(vec), _dt(vec) if vec is not None else F32, M, d,
+                                        _stream()), "rl_residual_inject")
+    _count()
+
+
+def softcap(logits: torch.Tensor, cap: float) -> None:
+    """logits = cap * tanh(logits / cap), in place (float32)."""
+    _need(logits, "logits", torch.float32)
+    _check(library().rl_softcap(logits.data_ptr(), logits.numel(), float(cap), _stream()), "rl_softcap")
+    _count()
+
+
+def sigmoid_gate(y: torch.Tensor, gate: torch.Tensor) -> None:
+    """y *= sigmoid(gate), in place; gate [M, n] may be a view with a wider row stride."""
+    _need(y, "y", contiguous=False); _need(gate, "gate", y.dtype, contiguous=False)
+    M, n = y.shape
+    assert gate.shape == (M, n) and y.stride(1) == 1 and gate.stride(1) == 1
+    _check(library().rl_sigmoid_gate(y.data_ptr(), y.stride(0) if M > 1 else n, gate.data_ptr(), gate.stride(0) if M > 1 else n,
+                                     _dt(y), M, n, _stream()), "rl_sigmoid_gate")
+    _count()
+
+
+def moe_route(x: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor], top: int,
+              ids: torch.Tensor, weights: torch.Tensor) -> None:
+    """Router of a mixture of experts: logits ``router @ x[m] + bias`` in 32-bit, the ``top`` largest
+    chosen (ties to the lower index), their weights the softmax over the chosen logits.
+    ids int32 [M, top], weights float32 [M, top], both in the order of falling logits."""
+    _need(x, "x", contiguous=False); _need(router, "router", x.dtype); _need(ids, "ids", torch.int32)
+    _need(weights, "weights", torch.float32)
+    M, d = x.shape
+    E = router.shape[0]
+    assert router.shape == (E, d) and ids.shape == (M, top) and weights.shape == (M, top) and x.stride(1) == 1
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        assert bias.numel() == E
+    _check(library().rl_moe_route(x.data_ptr(), x.stride(0) if M > 1 else d, router.data_ptr(), _ptr(bias), _dt(x), M, d, E,
+                                  int(top), ids.data_ptr(), weights.data_ptr(), _stream()), "rl_moe_route")
+    _count()
+
+
+def moe_experts(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+                residual: torch.Tensor) -> None:
+    """residual[m] += sum_c weights[m, c] * down[e] (silu(gate[e] x[m]) * (up[e] x[m])), e = ids[m, c], on the
+    CUDA cores (any sizes, float32 or bfloat16 storage).  gate_up: [E, 2, F, d] (an expert's gate rows, then
+    its up rows), down: [E, d, F]."""
+    _need(x, "x", contiguous=False); _need(gate_up, "gate_up", x.dtype); _need(down, "down", x.dtype)
+    _need(ids, "ids", torch.int32); _need(weights, "weights", torch.float32); _need(residual, "residual", torch.float32)
+    M, d = x.shape
+    E, two, F, d2 = gate_up.shape
+    top = ids.shape[1]
+    assert two == 2 and d2 == d and down.shape == (E, d, F) and residual.shape == (M, d) and x.stride(1) == 1
+    assert ids.shape == (M, top) and weights.shape == (M, top)
+    h = torch.empty((M * top, F), dtype=x.dtype, device=x.device)
+    _check(library().rl_moe_experts(x.data_ptr(), x.stride(0) if M > 1 else d, gate_up.data_ptr(), down.data_ptr(), _dt(x),
+                                    ids.data_ptr(), weights.data_ptr(), M, d, F, E, top, h.data_ptr(), residual.data_ptr(),
+                                    _stream()), "rl_moe_experts")
+    _count(2)
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,
             rows: Optional[torch.Tensor] = None) -> None:
     """out[r] = rms_norm(x[rows[r]] if rows is given else x[r]) * weight."""
@@ -258,9 +356,11 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slot_of_token: tor
 def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
                    slot_of_token: torch.Tensor, positions: torch.Tensor, out: torch.Tensor,
                    num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0,
-                   value_dim: Optional[int] = None) -> None:
+                   value_dim: Optional[int] = None, sink: bool = False, gate: Optional[torch.Tensor] = None) -> None:
     """q: [M, >= H*hd] (a view into the qkv buffer is fine), out: [M, H*vd] where vd is
-    ``value_dim`` (default: head_dim), the width of a value head."""
+    ``value_dim`` (default: head_dim), the width of a value head.  ``sink``: the softmax's
+    denominator has one more term of score 0 (and no value).  ``gate`` [M, H*vd] (a view is
+    fine): the output is multiplied by sigmoid(gate) before it is stored."""
     vd = head_dim if value_dim is None else value_dim
     _need(q, "q", contiguous=False); _need(k_pool, "k_pool", q.dtype); _need(v_pool, "v_pool", q.dtype)
     _need(out, "out", q.dtype); _need(page_table, "page_table", torch.int32)
@@ -268,10 +368,16 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
     M = q.shape[0]
     assert q.stride(1) == 1
     ldq = q.stride(0) if M > 1 else num_heads * head_dim
-    _check(library().rl_attention_simt(
+    ldg = 0
+    if gate is not None:
+        _need(gate, "gate", q.dtype, contiguous=False)
+        assert gate.shape == (M, num_heads * vd) and gate.stride(1) == 1
+        ldg = gate.stride(0) if M > 1 else num_heads * vd
+    _check(library().rl_attention_simt_gated(
         q.data_ptr(), ldq, k_pool.data_ptr(), v_pool.data_ptr(), _dt(q), page_table.data_ptr(),
         page_table.shape[1], slot_of_token.data_ptr(), positions.data_ptr(), out.data_ptr(), out.stride(0),
-        M, num_heads, num_kv_heads, head_dim, vd, float(scale), int(window), _stream()), "rl_attention_simt")
+        M, num_heads, num_kv_heads, head_dim, vd, float(scale), int(window), int(bool(sink)), _ptr(gate), ldg, _stream()),
+        "rl_attention_simt")
     _count()
 
 
@@ -727,15 +833,17 @@ def attention_prefill_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
 # ----------------------------------------------------------------------------- attention dispatch
 def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
               step, out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-              window: int = 0, value_dim: Optional[int] = None) -> None:
+              window: int = 0, value_dim: Optional[int] = None, sink: bool = False,
+              gate: Optional[torch.Tensor] = None) -> None:
     """Attention of the step's tokens over the cache; picks the kernel for the
     dtype and the shape of the step.  ``step`` carries positions, slots and
     sequence boundaries (engine.step.StepState).  Value heads of another width than the
     key heads (``value_dim``) run on the any-shape kernel; the tensor-core kernels take
-    one width for both."""
-    if value_dim is not None and value_dim != head_dim:
+    one width for both.  ``sink``: one more term of score 0 in the softmax's denominator.
+    ``gate`` [M, H*vd]: the output is multiplied by sigmoid(gate)."""
+    if (value_dim is not None and value_dim != head_dim) or sink or gate is not None:
         attention_simt(q, k_pool, v_pool, page_table, step.slot_of_token, step.positions, out,
-                       num_heads, num_kv_heads, head_dim, scale, window, value_dim=value_dim)
+                       num_heads, num_kv_heads, head_dim, scale, window, value_dim=value_dim, sink=sink, gate=gate)
         return
     if step.is_decode and attention_decode_supported(q.dtype, num_heads, num_kv_heads, head_dim):
         splits = decode_splits(q.shape[0], num_kv_heads)

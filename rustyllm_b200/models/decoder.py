@@ -54,6 +54,12 @@ class DecoderModel:
                                          feed_forward=ff, feed_forward_norm=ff_norm, **ls.block.params))
         self.final_norm = build_part("norm", spec.final_norm, runtime)
         self.head = build_part("head", spec.head, runtime)
+        # additions to the residual stream between layers, by the place of the run they stand before
+        self.inject_parts = [build_part("inject", ps, runtime) for ps in spec.inject_parts]
+        self.injections: Dict[int, list] = {}
+        for inj in spec.injections:
+            self.injections.setdefault(inj.before_run, []).append((self.inject_parts[inj.part], dict(inj.args)))
+        self._keep_embedded = any(getattr(p, "needs_embedding_output", False) for p in self.inject_parts) and bool(self.injections)
 
         # cache entries along the schedule
         self.run_entry: List[Tuple[int, bool]] = []   # per schedule position: (entry, writes)
@@ -74,6 +80,8 @@ class DecoderModel:
         _collect_params("embedding", self.embedding, self._params)
         for i, b in enumerate(self.blocks):
             _collect_params(f"layers.{i}", b, self._params)
+        for i, p in enumerate(self.inject_parts):
+            _collect_params(f"inject.{i}", p, self._params)
         _collect_params("final_norm", self.final_norm, self._params)
         _collect_params("head", self.head, self._params)
 
@@ -81,7 +89,7 @@ class DecoderModel:
     def graph_capturable(self) -> bool:
         def ok(part: Part) -> bool:
             return part.graph_capturable and all(ok(p) for p in part.sub_parts().values())
-        return all(ok(p) for p in [self.embedding, self.final_norm, self.head] + self.blocks)
+        return all(ok(p) for p in [self.embedding, self.final_norm, self.head] + self.blocks + self.inject_parts)
 
     # ------------------------------------------------------------------ parameters
     def param_specs(self) -> Dict[str, ParamSpec]:
@@ -138,9 +146,15 @@ class DecoderModel:
         if nat is not None:
             return nat.forward(step)
         x = self.embedding.forward(step)
+        embedded = None
+        if self._keep_embedded:      # the stream as the embedding leaves it, for parts that add it again later
+            embedded = torch.empty_like(x)
+            embedded.copy_(x)
         schedule = self.spec.schedule
         pending = None      # the next block's first norm, started by the block in front of it
         for pos, li in enumerate(schedule):
+            for part, args in self.injections.get(pos, ()):
+                part.forward(x, embedded, step, **args)
             entry, writes = self.run_entry[pos]
             where = cache.entry_group[entry]
             view = CacheView(
@@ -151,7 +165,9 @@ class DecoderModel:
             block = self.blocks[li]
             if block.folds_norms:
                 nxt = self.blocks[schedule[pos + 1]] if pos + 1 < len(schedule) else None
-                want = nxt.first_norm_request(x.shape[0]) if nxt is not None and nxt.folds_norms else None
+                # a norm is not started across an injection: the stream changes between the two layers
+                want = nxt.first_norm_request(x.shape[0]) if nxt is not None and nxt.folds_norms \
+                    and (pos + 1) not in self.injections else None
                 pending = block.forward(x, step, view, pending=pending, next_norm=want)
             else:
                 block.forward(x, step, view)

@@ -70,6 +70,8 @@ def eligible(model, cache) -> bool:
     from .parts.rope import RotaryEmbedding
     if model.runtime.compute_dtype != torch.bfloat16 or model.runtime.device.type != "cuda" or cache.dtype != torch.bfloat16:
         return False
+    if model.injections or model.head.softcap is not None:
+        return False
     if type(model.embedding) is not TokenEmbedding or type(model.head) is not LMHead or type(model.final_norm) is not RMSNorm:
         return False
     if not (_matrix_ok(model.embedding.weight) and _matrix_ok(model.head.weight) and _vector_ok(model.final_norm.weight)):
@@ -80,6 +82,8 @@ def eligible(model, cache) -> bool:
         if type(b.mixer_norm) is not RMSNorm or type(b.feed_forward_norm) is not RMSNorm or not isinstance(b.mixer.position, RotaryEmbedding):
             return False
         a, f = b.mixer, b.feed_forward
+        if a.sink or a.gated:
+            return False
         if not (f.interleaved and _matrix_ok(a.wqkv) and _matrix_ok(a.wo) and _matrix_ok(f.wgu) and _matrix_ok(f.wdown)):
             return False
         if not all(_vector_ok(v) for v in (a.bqkv, a.bo, f.bgu, f.bdown, b.mixer_norm.weight, b.feed_forward_norm.weight)):

@@ -4,7 +4,11 @@ Per layer, in the reference's order (SimonWaldherr/RustyLLM src/model.rs:7207-73
 q = Wq xn, k = Wk xn, v = Wv xn (+ biases if the tensors exist); rotary encoding of
 q and k; K[pos] = k, V[pos] = v; per query head h with KV head g = h / (H/G):
 softmax over t <= pos of (q_h . K[t, g]) / sqrt(head_dim), times V; then
-x += Wo attn.  Here Wq, Wk, Wv are one matrix [(H + 2G) hd x d] so that one product
+x += Wo attn.  Options other designs use, each a constructor parameter: another score
+scale than 1/sqrt(head_dim) (``scale``); a sliding ``window`` (a query at position i reads
+positions j with 0 <= i - j < window); a ``sink`` (the softmax's denominator has one more
+term, of score 0 and without a value: p_j = e^{s_j} / (1 + sum_t e^{s_t})); an output gate
+(``names["g"]``: the concatenated heads are multiplied by sigmoid(Wg xn) before Wo).  Here Wq, Wk, Wv are one matrix [(H + 2G) hd x d] so that one product
 serves all three, rotation and cache write are one kernel, and all tokens of the
 step (several sequences, prompt or single tokens) run together.
 """
@@ -27,7 +31,8 @@ from .registry import build_part, register_mixer
 class GQAttention(Mixer):
     def __init__(self, runtime: Runtime, hidden_size: int, num_heads: int, num_kv_heads: int,
                  head_dim: int, position: PartSpec, names: Dict[str, str], bias: bool = False,
-                 window: Optional[int] = None, value_dim: Optional[int] = None):
+                 window: Optional[int] = None, value_dim: Optional[int] = None,
+                 scale: Optional[float] = None, sink: bool = False):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads are no multiple of {num_kv_heads} KV heads")
         if head_dim % 2 or not (0 < head_dim <= 256):
@@ -41,20 +46,24 @@ class GQAttention(Mixer):
         self.runtime = runtime
         self.d, self.H, self.G, self.hd = hidden_size, num_heads, num_kv_heads, head_dim
         self.bias = bias
+        if bias and "g" in names:
+            raise ValueError("an output gate with biases is not built")
         self.window = window
         self.names = names
-        self.scale = 1.0 / math.sqrt(head_dim)     # src/model.rs:7239
+        self.scale = 1.0 / math.sqrt(head_dim) if scale is None else float(scale)     # src/model.rs:7239
+        self.sink = bool(sink)
+        self.gated = "g" in names          # an output gate: its rows ride behind q, k, v in the one product
         self.position = build_part("position", position, runtime)
         self.wqkv = self.wo = self.bqkv = self.bo = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         d, H, G, hd, vd, n = self.d, self.H, self.G, self.hd, self.vd, self.names
-        specs = {
-            "wqkv": ParamSpec((ParamSource(n["q"] + ".weight", (H * hd, d)),
-                               ParamSource(n["k"] + ".weight", (G * hd, d)),
-                               ParamSource(n["v"] + ".weight", (G * vd, d)))),
-            "wo": ParamSpec((ParamSource(n["o"] + ".weight", (d, H * vd)),)),
-        }
+        sfx = n.get("suffix", ".weight")     # what follows a projection's name in the checkpoint
+        qkv = (ParamSource(n["q"] + sfx, (H * hd, d)), ParamSource(n["k"] + sfx, (G * hd, d)),
+               ParamSource(n["v"] + sfx, (G * vd, d)))
+        if self.gated:
+            qkv += (ParamSource(n["g"] + sfx, (H * vd, d)),)
+        specs = {"wqkv": ParamSpec(qkv), "wo": ParamSpec((ParamSource(n["o"] + sfx, (d, H * vd)),))}
         if self.bias:
             specs["bqkv"] = ParamSpec((ParamSource(n["q"] + ".bias", (H * hd,)),
                                        ParamSource(n["k"] + ".bias", (G * hd,)),
@@ -74,12 +83,13 @@ class GQAttention(Mixer):
         H, G, hd, vd = self.H, self.G, self.hd, self.vd
         M = xn.shape[0]
         dt = xn.dtype
-        qkv = torch.empty((M, (H + G) * hd + G * vd), dtype=dt, device=xn.device)
+        n_qkv = (H + G) * hd + G * vd
+        qkv = torch.empty((M, n_qkv + (H * vd if self.gated else 0)), dtype=dt, device=xn.device)
         group, layer = cache.kv_group, cache.kv_layer
         k_pool, v_pool = group.k_pool(layer), group.v_pool(layer)
         pos = self.position
         x = xn.weighted if isinstance(xn, NormedInput) else xn
-        if (dt == torch.bfloat16 and vd == hd and self.wqkv.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16
+        if (dt == torch.bfloat16 and vd == hd and not self.gated and self.wqkv.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16
                 and K.gemm_tc_qkv_rope_supported(x, self.wqkv, H, G, hd, pos.rotary_dim)):
             # few tokens: rotation and cache write ride in the product's epilogue
             kw = dict(row_sumsq=xn.sumsq, row_eps=xn.eps) if isinstance(xn, NormedInput) else {}
@@ -93,5 +103,5 @@ class GQAttention(Mixer):
                             k_pool if cache.writes else None, v_pool if cache.writes else None, value_dim=vd)
         attn = torch.empty((M, H * vd), dtype=dt, device=xn.device)
         K.attention(qkv, k_pool, v_pool, group.page_table, step, attn, H, G, hd, self.scale,
-                    self.window or 0, value_dim=vd)
+                    self.window or 0, value_dim=vd, sink=self.sink, gate=qkv[:, n_qkv:] if self.gated else None)
         return linear(attn, self.wo, residual, OUT_ADD_F32, self.bo, then_norm=then_norm)

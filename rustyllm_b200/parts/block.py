@@ -34,6 +34,12 @@ class PreNormBlock(Block):
         # front starts it, the one behind finishes it) where both parts can; otherwise the
         # norm part runs its own kernel.
         xn = pending if pending is not None else self.mixer_norm.forward(x, dt)
+        if getattr(self.feed_forward, "absent", False):
+            # a layer of a mixer alone: its last product may start the next layer's norm
+            if getattr(self.mixer, "folds_norms", False):
+                return self.mixer.forward(xn, x, step, cache, then_norm=next_norm)
+            self.mixer.forward(xn, x, step, cache)
+            return None
         started = None
         if getattr(self.mixer, "folds_norms", False):
             want = None

@@ -39,10 +39,37 @@ class TokenEmbedding(Part):
         return x
 
 
+@register("embedding", "token_position_embedding")
+class TokenPositionEmbedding(TokenEmbedding):
+    """Token embedding plus a learned absolute position vector: x = E[token] + P[position], neither
+    scaled, summed in 32-bit.  Positions count from 0 in each sequence; the table has
+    ``max_positions`` rows."""
+
+    def __init__(self, runtime: Runtime, vocab_size: int, hidden_size: int, name: str, max_positions: int,
+                 position_name: str):
+        super().__init__(runtime, vocab_size, hidden_size, name)
+        self.P, self.position_name = max_positions, position_name
+        self.positions: Optional[torch.Tensor] = None
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        specs = super().param_specs()
+        specs["positions"] = ParamSpec((ParamSource(self.position_name, (self.P, self.d)),), role="table")
+        return specs
+
+    def forward(self, step) -> torch.Tensor:
+        tokens = step.tokens
+        x = torch.empty((tokens.numel(), self.d), dtype=torch.float32, device=tokens.device)
+        K.embedding_pos(self.weight, self.positions, tokens, step.positions, x, self.bad_token)
+        return x
+
+
 @register("head", "lm_head")
 class LMHead(Part):
     def __init__(self, runtime: Runtime, vocab_size: int, hidden_size: int, name: str,
-                 tied_to: Optional[str] = None):
+                 tied_to: Optional[str] = None, softcap: Optional[float] = None):
+        if softcap is not None and not softcap > 0:
+            raise ValueError(f"softcap {softcap} must be > 0 or None")
+        self.softcap = None if softcap is None else float(softcap)    # logits <- cap * tanh(logits / cap)
         self.runtime = runtime
         self.V, self.d, self.name, self.tied_to = vocab_size, hidden_size, name, tied_to
         self.weight: Optional[torch.Tensor] = None
@@ -55,4 +82,6 @@ class LMHead(Part):
         """xn: [W, d] compute dtype -> float32 logits [W, V]."""
         logits = torch.empty((xn.shape[0], self.V), dtype=torch.float32, device=xn.device)
         linear(xn, self.weight, logits, OUT_F32)
+        if self.softcap is not None:
+            K.softcap(logits, self.softcap)
         return logits

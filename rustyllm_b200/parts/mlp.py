@@ -37,10 +37,11 @@ class GatedMLP(FeedForward):
     def param_specs(self) -> Dict[str, ParamSpec]:
         d, I, n = self.d, self.I, self.names
         layout = "interleave" if self.interleaved else "concat"
+        sfx = n.get("suffix", ".weight")     # what follows a projection's name in the checkpoint
         specs = {
-            "wgu": ParamSpec((ParamSource(n["gate"] + ".weight", (I, d)),
-                              ParamSource(n["up"] + ".weight", (I, d))), layout=layout),
-            "wdown": ParamSpec((ParamSource(n["down"] + ".weight", (d, I)),)),
+            "wgu": ParamSpec((ParamSource(n["gate"] + sfx, (I, d)),
+                              ParamSource(n["up"] + sfx, (I, d))), layout=layout),
+            "wdown": ParamSpec((ParamSource(n["down"] + sfx, (d, I)),)),
         }
         if self.bias:
             specs["bgu"] = ParamSpec((ParamSource(n["gate"] + ".bias", (I,)),
@@ -68,3 +69,15 @@ class GatedMLP(FeedForward):
             linear(xn, self.wgu, gu, OUT_SAME, self.bgu)
             K.swiglu(gu, h, interleaved=self.interleaved)
         return linear(h, self.wdown, residual, OUT_ADD_F32, self.bdown, then_norm=then_norm)
+
+
+@register_feed_forward("none")
+class NoFeedForward(FeedForward):
+    """A layer without a feed-forward: the block skips its second half."""
+    absent = True
+
+    def __init__(self, runtime: Runtime):
+        self.runtime = runtime
+
+    def forward(self, xn, residual: torch.Tensor, step) -> None:
+        return None

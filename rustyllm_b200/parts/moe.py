@@ -1,0 +1,71 @@
+"""Mixture-of-experts feed-forward: a router picks ``top`` of ``experts`` small gated feed-forwards
+per token; their outputs are summed with the router's weights; a shared expert, where the model
+has one, runs for every token and is added.
+
+    z = Wr xn + b                       (32-bit)
+    C = the ``top`` experts of largest z; w_c = softmax over z restricted to C
+    x += sum_{c in C} w_c * Wdown_c (silu(Wgate_c xn) * (Wup_c xn))  [+ shared(xn)]
+
+The experts' matrices are stacked: gate and up as [E, 2, F, d], down as [E, d, F], so one kernel
+indexes any expert.  The shared expert is an ordinary gated feed-forward part of its own sizes.
+"""
+from __future__ import annotations
+
+from typing import Dict, Optional
+
+import torch
+
+from .. import kernels as K
+from ..config.spec import ParamSource, ParamSpec, PartSpec
+from .base import FeedForward, Runtime
+from .registry import build_part, register_feed_forward
+
+
+@register_feed_forward("moe_mlp")
+class MoEMLP(FeedForward):
+    def __init__(self, runtime: Runtime, hidden_size: int, expert_size: int, num_experts: int, top: int,
+                 names: Dict[str, str], router_bias: bool = True, shared: Optional[PartSpec] = None):
+        """``names``: "router" (the router's matrix; its bias is that name + ``names["bias_suffix"]``),
+        "expert" (a format string with ``{e}`` for the expert's number, giving the prefix of its
+        "gate", "up" and "down" tensors), "suffix" (what follows a projection's name)."""
+        if not (0 < top <= num_experts):
+            raise ValueError(f"top {top} must lie in [1, {num_experts}]")
+        if top > 32:
+            raise ValueError("at most 32 experts a token")
+        self.runtime = runtime
+        self.d, self.F, self.E, self.top = hidden_size, expert_size, num_experts, top
+        self.names = names
+        self.router_bias = router_bias
+        self.shared = build_part("feed_forward", shared, runtime) if shared is not None else None
+        self.router = self.router_b = self.wgu = self.wdown = None
+
+    def sub_parts(self):
+        return {"shared": self.shared} if self.shared is not None else {}
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        d, F, E, n = self.d, self.F, self.E, self.names
+        sfx = n.get("suffix", ".weight")
+        ex = [n["expert"].format(e=e) for e in range(E)]
+        gu = tuple(ParamSource(p + "." + part + sfx, (F, d)) for p in ex for part in ("gate", "up"))
+        specs = {
+            "router": ParamSpec((ParamSource(n["router"] + sfx, (E, d)),)),
+            "wgu": ParamSpec(gu),                                                   # [E * 2 * F, d]
+            "wdown": ParamSpec(tuple(ParamSource(p + ".down" + sfx, (d, F)) for p in ex)),   # [E * d, F]
+        }
+        if self.router_bias:
+            specs["router_b"] = ParamSpec((ParamSource(n["router"] + n.get("bias_suffix", ".bias"), (E,)),),
+                                          role="vector", init="zeros")
+        return specs
+
+    def forward(self, xn: torch.Tensor, residual: torch.Tensor, step) -> None:
+        M = xn.shape[0]
+        ids = torch.empty((M, self.top), dtype=torch.int32, device=xn.device)
+        weights = torch.empty((M, self.top), dtype=torch.float32, device=xn.device)
+        router = self.router
+        if router.dtype != xn.dtype:
+            raise K.KernelError(f"the router's matrix is {router.dtype} in a {xn.dtype} run")
+        K.moe_route(xn, router, self.router_b, self.top, ids, weights)
+        K.moe_experts(xn, self.wgu.view(self.E, 2, self.F, self.d), self.wdown.view(self.E, self.d, self.F),
+                      ids, weights, residual)
+        if self.shared is not None:
+            self.shared.forward(xn, residual, step)

@@ -36,3 +36,14 @@ class RMSNorm(Norm):
 
     def request(self) -> Optional[NormRequest]:
         return NormRequest(self.weight, self.eps) if self.weight is not None else None
+
+
+@register_norm("none")
+class NoNorm(Norm):
+    """The norm in front of a part that does not exist (a layer without a feed-forward)."""
+
+    def __init__(self, runtime: Runtime):
+        self.runtime = runtime
+
+    def forward(self, x, out_dtype, rows=None):
+        raise RuntimeError("a norm of kind 'none' stands in front of nothing and is never run")

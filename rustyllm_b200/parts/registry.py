@@ -14,7 +14,7 @@ from ..config.spec import PartSpec
 
 _REGISTRIES: Dict[str, Dict[str, Callable]] = {
     "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {},
-    "embedding": {}, "head": {},
+    "embedding": {}, "head": {}, "inject": {},
 }
 
 
