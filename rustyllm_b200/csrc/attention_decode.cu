@@ -185,6 +185,27 @@ struct DecSmem {
   static constexpr int BYTES = RING_BYTES > MERGE_BYTES + RESULT_BYTES ? RING_BYTES : MERGE_BYTES + RESULT_BYTES;
 };
 
+// How a (sequence, head) row is finished once maximum M, denominator L and output O over all its
+// keys are known (M in the exp2 domain).  sink: the denominator has one more term of score 0 and no
+// value, p_j = e^{s_j} / (1 + sum e^{s_t}); gate: the output is multiplied by sigmoid(gate[b, h*HD + d]).
+struct DecFinish {
+  int sink;
+  const __nv_bfloat16* gate;
+  int ldg;
+};
+
+__device__ __forceinline__ float dec_finish(float O, float L, float M, const DecFinish& f, int b, int col) {
+  if (f.sink) {
+    const float M2 = fmaxf(M, 0.f);
+    const float w = exp2f(M - M2);          // exp2(-inf) = 0: a row without keys is the sink alone
+    O *= w;
+    L = L * w + exp2f(-M2);
+  }
+  float o = L > 0.f ? O / L : 0.f;
+  if (f.gate) o *= 1.0f / (1.0f + expf(-__bfloat162float(f.gate[(size_t)b * f.ldg + col])));
+  return o;
+}
+
 template <int HD>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv_bfloat16* __restrict__ k_pool,
@@ -192,7 +213,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
                         const int* __restrict__ seq_slots, const int* __restrict__ kv_lens,
                         const int4* __restrict__ plan, __nv_bfloat16* __restrict__ out, int ldo,
                         float* __restrict__ part_o, float* __restrict__ part_ml, int H, int G, float scale_log2e,
-                        int window, int even_splits) {
+                        int window, int even_splits, DecFinish fin) {
   constexpr int NT = HD / 8;        // output n-tiles of 8 columns
   constexpr int KS = HD / 16;       // k-steps of the Q.K product
   extern __shared__ __align__(128) uint8_t dec_smem[];
@@ -394,7 +415,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
     }
     const int h = gkv * m + r;
     if (direct) {
-      out[(size_t)b * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+      out[(size_t)b * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(dec_finish(O, L, M, fin, b, h * HD + d));
     } else if (clustered) {
       float* c_o = reinterpret_cast<float*>(dec_smem + DecSmem<HD>::MERGE_BYTES);
       c_o[r * HD + d] = O;
@@ -423,7 +444,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
         L += dec_peer_f32(c_o + 16 * HD + 16 + r, c) * wgt;
         O += dec_peer_f32(c_o + r * HD + d, c) * wgt;
       }
-      out[(size_t)b * ldo + (size_t)(gkv * m + r) * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+      out[(size_t)b * ldo + (size_t)(gkv * m + r) * HD + d] = __float2bfloat16_rn(dec_finish(O, L, M, fin, b, (gkv * m + r) * HD + d));
     }
     dec_cluster_sync();      // nobody leaves while its shared memory may still be read
   }
@@ -433,7 +454,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
 template <int HD>
 __global__ void attention_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                                 const int2* __restrict__ plan_seqs, int even_splits,
-                                                __nv_bfloat16* __restrict__ out, int ldo, int H) {
+                                                __nv_bfloat16* __restrict__ out, int ldo, int H, DecFinish fin) {
   rl_pdl_trigger();
   const int h = blockIdx.x, b = blockIdx.y;
   int first = b * even_splits, count = even_splits;
@@ -465,7 +486,7 @@ __global__ void attention_decode_combine_kernel(const float* __restrict__ part_o
       L += ml[s].y * wgt;
       O += o[s] * wgt;
     }
-    out[(size_t)b * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+    out[(size_t)b * ldo + (size_t)h * HD + d] = __float2bfloat16_rn(dec_finish(O, L, M, fin, b, h * HD + d));
     return;
   }
   float M = -INFINITY;
@@ -480,7 +501,7 @@ __global__ void attention_decode_combine_kernel(const float* __restrict__ part_o
       L += part_ml[2 * p + 1] * wgt;
       O += part_o[p * HD + dd] * wgt;
     }
-    out[(size_t)b * ldo + (size_t)h * HD + dd] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+    out[(size_t)b * ldo + (size_t)h * HD + dd] = __float2bfloat16_rn(dec_finish(O, L, M, fin, b, h * HD + dd));
   }
 }
 
@@ -488,7 +509,7 @@ template <int HD>
 static int launch_decode(const void* q, int ldq, const void* k_pool, const void* v_pool, const int* page_table,
                          int max_pages, const int* seq_slots, const int* kv_lens, void* out, int ldo,
                          float* part_o, float* part_ml, const int* plan, int B, int H, int G, float scale, int window,
-                         int num_splits, cudaStream_t stream) {
+                         int num_splits, DecFinish fin, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, DecSmem<HD>::BYTES);
@@ -521,7 +542,7 @@ static int launch_decode(const void* q, int ldq, const void* k_pool, const void*
     cudaError_t e = cudaLaunchKernelEx(&cfg, attention_decode_kernel<HD>,
         (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_table, max_pages,
         seq_slots, kv_lens, (const int4*)nullptr, (__nv_bfloat16*)out, ldo, (float*)nullptr, (float*)nullptr, H, G,
-        scale * 1.4426950408889634f, window, num_splits);
+        scale * 1.4426950408889634f, window, num_splits, fin);
     RL_REQUIRE(e == cudaSuccess, "rl_attention_decode: cluster launch failed: %s", cudaGetErrorString(e));
     RL_LAUNCH_CHECK("rl_attention_decode");
     return RL_OK;
@@ -530,11 +551,11 @@ static int launch_decode(const void* q, int ldq, const void* k_pool, const void*
   rl_launch_pdl(attention_decode_kernel<HD>, grid, dim3(DEC_WARPS * 32), (size_t)DecSmem<HD>::BYTES, stream,
       (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_table, max_pages,
       seq_slots, kv_lens, entries, (__nv_bfloat16*)out, ldo, part_o, part_ml, H, G, scale * 1.4426950408889634f, window,
-      num_splits);
+      num_splits, fin);
   RL_LAUNCH_CHECK("rl_attention_decode");
   if (num_splits > 1) {
     rl_launch_pdl(attention_decode_combine_kernel<HD>, dim3(H, B), dim3(HD), 0, stream,
-                  (const float*)part_o, (const float*)part_ml, seqs, num_splits, (__nv_bfloat16*)out, ldo, H);
+                  (const float*)part_o, (const float*)part_ml, seqs, num_splits, (__nv_bfloat16*)out, ldo, H, fin);
     RL_LAUNCH_CHECK("rl_attention_decode (combine)");
   }
   return RL_OK;
@@ -629,11 +650,17 @@ extern "C" int rl_attention_decode_order(const int* seq_slots, const int* kv_len
 // equal chunks whatever its length (right for one sequence, or for sequences of like lengths).  Null scratch with 2, 4 or 8
 // splits and no plan: the chunks of a sequence run as a thread-block cluster and combine
 // through distributed shared memory (no scratch, no second kernel).
-extern "C" int rl_attention_decode(const void* q, int ldq, const void* k_pool, const void* v_pool,
-                                   const int* page_table, int max_pages, const int* seq_slots, const int* kv_lens,
-                                   void* out, int ldo, float* scratch, const int* plan, int num_seqs, int num_heads,
-                                   int num_kv_heads, int head_dim, float scale, int window, int num_splits,
-                                   cudaStream_t stream) {
+//
+// sink != 0: the softmax's denominator has one more term, of score 0 and without a value.  gate (may be
+// null): bf16 [num_seqs, ldg]; head h's output is multiplied element by element with
+// sigmoid(gate[b, h*head_dim + i]) before it is stored.
+extern "C" int rl_attention_decode_gated(const void* q, int ldq, const void* k_pool, const void* v_pool,
+                                         const int* page_table, int max_pages, const int* seq_slots, const int* kv_lens,
+                                         void* out, int ldo, float* scratch, const int* plan, int num_seqs, int num_heads,
+                                         int num_kv_heads, int head_dim, float scale, int window, int num_splits,
+                                         int sink, const void* gate, int ldg, cudaStream_t stream) {
+  RL_REQUIRE(gate == nullptr || ldg >= num_heads * head_dim, "rl_attention_decode: the gate's row stride is too small");
+  const DecFinish fin = {sink, (const __nv_bfloat16*)gate, ldg};
   RL_REQUIRE(rl_attention_decode_supported(num_heads, num_kv_heads, head_dim),
              "rl_attention_decode: unsupported shape (heads %d, KV heads %d, head_dim %d): needs head_dim 64 or 128 "
              "and at most 16 heads per KV head", num_heads, num_kv_heads, head_dim);
@@ -654,9 +681,18 @@ extern "C" int rl_attention_decode(const void* q, int ldq, const void* k_pool, c
   float* part_ml = scratch ? scratch + parts * head_dim : nullptr;
   if (head_dim == 64)
     return launch_decode<64>(q, ldq, k_pool, v_pool, page_table, max_pages, seq_slots, kv_lens, out, ldo, part_o,
-                             part_ml, plan, num_seqs, num_heads, num_kv_heads, scale, window, num_splits, stream);
+                             part_ml, plan, num_seqs, num_heads, num_kv_heads, scale, window, num_splits, fin, stream);
   return launch_decode<128>(q, ldq, k_pool, v_pool, page_table, max_pages, seq_slots, kv_lens, out, ldo, part_o,
-                            part_ml, plan, num_seqs, num_heads, num_kv_heads, scale, window, num_splits, stream);
+                            part_ml, plan, num_seqs, num_heads, num_kv_heads, scale, window, num_splits, fin, stream);
+}
+
+extern "C" int rl_attention_decode(const void* q, int ldq, const void* k_pool, const void* v_pool,
+                                   const int* page_table, int max_pages, const int* seq_slots, const int* kv_lens,
+                                   void* out, int ldo, float* scratch, const int* plan, int num_seqs, int num_heads,
+                                   int num_kv_heads, int head_dim, float scale, int window, int num_splits,
+                                   cudaStream_t stream) {
+  return rl_attention_decode_gated(q, ldq, k_pool, v_pool, page_table, max_pages, seq_slots, kv_lens, out, ldo, scratch, plan,
+                                   num_seqs, num_heads, num_kv_heads, head_dim, scale, window, num_splits, 0, nullptr, 0, stream);
 }
 
 // ------------------------------------------------------------------ entry point that allocates nothing

@@ -56,7 +56,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __n
                          const __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ page_table, int max_pages,
                          const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slots,
                          const int* __restrict__ kv_lens, int num_seqs, __nv_bfloat16* __restrict__ out, int ldo,
-                         int H, int G, float scale_log2e, int window) {
+                         int H, int G, float scale_log2e, int window, int sink,
+                         const __nv_bfloat16* __restrict__ gate, int ldg) {
   constexpr int ROW_BYTES = HD * 2;
   constexpr int CHUNKS = HD / 8;                   // 16-byte chunks per row
   constexpr int TILE_BYTES = PF_KTILE * ROW_BYTES;
@@ -221,20 +222,49 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __n
   pf_wait<0>();
 
   // ---- write the 16 x HD outputs of this warp ----
-  const float inv_lo = l_run[0] > 0.f ? 1.0f / l_run[0] : 0.f, inv_hi = l_run[1] > 0.f ? 1.0f / l_run[1] : 0.f;
+  float inv[2];
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    if (sink) {
+      // one more term in the denominator, of score 0 and without a value: exp2(0 - max) beside the keys' sum
+      const float m2 = fmaxf(m_run[half], 0.f);
+      const float w = exp2f(m_run[half] - m2);          // exp2(-inf) = 0: a row without keys gives 0
+      inv[half] = w / (l_run[half] * w + exp2f(-m2));
+    } else {
+      inv[half] = l_run[half] > 0.f ? 1.0f / l_run[half] : 0.f;
+    }
+  }
+  const float inv_lo = inv[0], inv_hi = inv[1];
   __nv_bfloat16* olo = out + (size_t)(row0 + qt0 + r_lo) * ldo + (size_t)h * HD;
   __nv_bfloat16* ohi = olo + (size_t)8 * ldo;
+  const __nv_bfloat16* glo = gate ? gate + (size_t)(row0 + qt0 + r_lo) * ldg + (size_t)h * HD : nullptr;
+  const __nv_bfloat16* ghi = gate ? glo + (size_t)8 * ldg : nullptr;
 #pragma unroll
   for (int j = 0; j < NT_O; ++j) {
-    if (r_lo < rows_here) *reinterpret_cast<uint32_t*>(olo + 8 * j + 2 * t4) = pf_pack(acc[j][0] * inv_lo, acc[j][1] * inv_lo);
-    if (r_hi < rows_here) *reinterpret_cast<uint32_t*>(ohi + 8 * j + 2 * t4) = pf_pack(acc[j][2] * inv_hi, acc[j][3] * inv_hi);
+    if (r_lo < rows_here) {
+      float a = acc[j][0] * inv_lo, b = acc[j][1] * inv_lo;
+      if (gate) {           // output gate: times sigmoid(gate), in 32-bit, before the one rounding to bf16
+        const float2 gg = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(glo + 8 * j + 2 * t4));
+        a *= 1.0f / (1.0f + expf(-gg.x)); b *= 1.0f / (1.0f + expf(-gg.y));
+      }
+      *reinterpret_cast<uint32_t*>(olo + 8 * j + 2 * t4) = pf_pack(a, b);
+    }
+    if (r_hi < rows_here) {
+      float a = acc[j][2] * inv_hi, b = acc[j][3] * inv_hi;
+      if (gate) {
+        const float2 gg = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(ghi + 8 * j + 2 * t4));
+        a *= 1.0f / (1.0f + expf(-gg.x)); b *= 1.0f / (1.0f + expf(-gg.y));
+      }
+      *reinterpret_cast<uint32_t*>(ohi + 8 * j + 2 * t4) = pf_pack(a, b);
+    }
   }
 }
 
 template <int HD>
 static int launch_prefill(const void* q, int ldq, const void* k_pool, const void* v_pool, const int* page_table,
                           int max_pages, const int* cu_seqlens, const int* seq_slots, const int* kv_lens, int num_seqs,
-                          int num_tiles, void* out, int ldo, int H, int G, float scale, int window, cudaStream_t stream) {
+                          int num_tiles, void* out, int ldo, int H, int G, float scale, int window, int sink, const void* gate,
+                          int ldg, cudaStream_t stream) {
   constexpr int SMEM = 2 * 2 * PF_KTILE * HD * 2;
   static bool configured = false;
   if (!configured) {
@@ -245,7 +275,8 @@ static int launch_prefill(const void* q, int ldq, const void* k_pool, const void
   dim3 grid(num_tiles, H);
   rl_launch_pdl(attention_prefill_kernel<HD>, grid, dim3(PF_WARPS * 32), (size_t)SMEM, stream,
       (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_table, max_pages,
-      cu_seqlens, seq_slots, kv_lens, num_seqs, (__nv_bfloat16*)out, ldo, H, G, scale * 1.4426950408889634f, window);
+      cu_seqlens, seq_slots, kv_lens, num_seqs, (__nv_bfloat16*)out, ldo, H, G, scale * 1.4426950408889634f, window,
+      sink, (const __nv_bfloat16*)gate, ldg);
   RL_LAUNCH_CHECK("rl_attention_prefill");
   return RL_OK;
 }
@@ -259,11 +290,15 @@ extern "C" int rl_attention_prefill_supported(int num_heads, int num_kv_heads, i
 // q: [M, ldq] bf16, the step's tokens packed by sequence (cu_seqlens: [B+1] offsets);
 // kv_lens[b] = length of sequence b after this step (its query tokens take the last
 // positions); num_tiles = sum over sequences of ceil(tokens / 64).  out: [M, ldo] bf16.
-extern "C" int rl_attention_prefill(const void* q, int ldq, const void* k_pool, const void* v_pool,
-                                    const int* page_table, int max_pages, const int* cu_seqlens,
-                                    const int* seq_slots, const int* kv_lens, int num_seqs, int num_tiles, void* out,
-                                    int ldo, int num_heads, int num_kv_heads, int head_dim, float scale, int window,
-                                    cudaStream_t stream) {
+// sink != 0: one more term of score 0 in the softmax's denominator.  gate (may be null): bf16 [M, ldg], the
+// output is multiplied by sigmoid(gate[m, h*head_dim + i]); ldg even, gate 4-byte aligned.
+extern "C" int rl_attention_prefill_gated(const void* q, int ldq, const void* k_pool, const void* v_pool,
+                                          const int* page_table, int max_pages, const int* cu_seqlens,
+                                          const int* seq_slots, const int* kv_lens, int num_seqs, int num_tiles, void* out,
+                                          int ldo, int num_heads, int num_kv_heads, int head_dim, float scale, int window,
+                                          int sink, const void* gate, int ldg, cudaStream_t stream) {
+  RL_REQUIRE(gate == nullptr || (ldg >= num_heads * head_dim && ldg % 2 == 0 && ((uintptr_t)gate & 3) == 0),
+             "rl_attention_prefill: the gate's row stride is too small or odd, or the gate is misaligned");
   RL_REQUIRE(rl_attention_prefill_supported(num_heads, num_kv_heads, head_dim),
              "rl_attention_prefill: unsupported shape (heads %d, KV heads %d, head_dim %d): needs head_dim 64 or 128",
              num_heads, num_kv_heads, head_dim);
@@ -276,7 +311,16 @@ extern "C" int rl_attention_prefill(const void* q, int ldq, const void* k_pool, 
   if (num_seqs == 0 || num_tiles == 0) return RL_OK;
   if (head_dim == 64)
     return launch_prefill<64>(q, ldq, k_pool, v_pool, page_table, max_pages, cu_seqlens, seq_slots, kv_lens, num_seqs,
-                              num_tiles, out, ldo, num_heads, num_kv_heads, scale, window, stream);
+                              num_tiles, out, ldo, num_heads, num_kv_heads, scale, window, sink, gate, ldg, stream);
   return launch_prefill<128>(q, ldq, k_pool, v_pool, page_table, max_pages, cu_seqlens, seq_slots, kv_lens, num_seqs,
-                             num_tiles, out, ldo, num_heads, num_kv_heads, scale, window, stream);
+                             num_tiles, out, ldo, num_heads, num_kv_heads, scale, window, sink, gate, ldg, stream);
+}
+
+extern "C" int rl_attention_prefill(const void* q, int ldq, const void* k_pool, const void* v_pool,
+                                    const int* page_table, int max_pages, const int* cu_seqlens,
+                                    const int* seq_slots, const int* kv_lens, int num_seqs, int num_tiles, void* out,
+                                    int ldo, int num_heads, int num_kv_heads, int head_dim, float scale, int window,
+                                    cudaStream_t stream) {
+  return rl_attention_prefill_gated(q, ldq, k_pool, v_pool, page_table, max_pages, cu_seqlens, seq_slots, kv_lens, num_seqs,
+                                    num_tiles, out, ldo, num_heads, num_kv_heads, head_dim, scale, window, 0, nullptr, 0, stream);
 }

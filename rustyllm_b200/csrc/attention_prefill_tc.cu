@@ -195,7 +195,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slots,
                             const int* __restrict__ kv_lens, int num_seqs, __nv_bfloat16* __restrict__ out, int ldo,
                             int H, int G, float scale_log2e, int window, int* __restrict__ err,
-                            const int* __restrict__ tile_order) {
+                            const int* __restrict__ tile_order, int sink, const __nv_bfloat16* __restrict__ gate, int ldg) {
   extern __shared__ uint8_t fa_smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)fa_smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* q_tile = smem;                                   // [2 halves][128 x 64]
@@ -550,8 +550,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const float w_mine = m_mine == -INFINITY ? 0.f : fa_exp2(m_mine - m_fin);
         const float w_other = m_other == -INFINITY ? 0.f : fa_exp2(m_other - m_fin);
         const float l_row = grp == 0 ? l_run * w_mine + l_other * w_other : l_other * w_other + l_run * w_mine;
-        const float inv = l_row > 0.f ? 1.0f / l_row : 0.f;
+        // sink: one more term in the denominator, of score 0 and without a value; O and the sums are in
+        // units of exp2(-m_fin), so the term is exp2(0 - m_fin) (a row without keys: 1 / inf = 0)
+        const float l_all = sink ? l_row + fa_exp2(-m_fin) : l_row;
+        const float inv = l_all > 0.f ? 1.0f / l_all : 0.f;
         __nv_bfloat16* orow = out + (size_t)(row0 + qt0 + r) * ldo + (size_t)h * HD + grp * OC;
+        const __nv_bfloat16* grow = gate ? gate + (size_t)(row0 + qt0 + r) * ldg + (size_t)h * HD + grp * OC : nullptr;
 #pragma unroll 1
         for (int c = 0; c < OC / 16; ++c) {
           uint32_t v[16];
@@ -559,9 +563,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           fa_wait_ld();
           if (r < rows_here) {
             uint32_t pk[8];
+            uint32_t gk[8];
+            if (gate) {        // output gate: 16 bf16 of this row, 16-byte aligned (checked on the host)
+              const uint4 g0 = *reinterpret_cast<const uint4*>(grow + c * 16), g1 = *reinterpret_cast<const uint4*>(grow + c * 16 + 8);
+              gk[0] = g0.x; gk[1] = g0.y; gk[2] = g0.z; gk[3] = g0.w; gk[4] = g1.x; gk[5] = g1.y; gk[6] = g1.z; gk[7] = g1.w;
+            }
 #pragma unroll
             for (int j = 0; j < 16; j += 2) {
-              __nv_bfloat162 o2 = __floats2bfloat162_rn(__uint_as_float(v[j]) * inv, __uint_as_float(v[j + 1]) * inv);
+              float a = __uint_as_float(v[j]) * inv, b = __uint_as_float(v[j + 1]) * inv;
+              if (gate) {      // times sigmoid(gate) in 32-bit, before the one rounding to bf16
+                const float2 gg = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&gk[j >> 1]));
+                a *= 1.0f / (1.0f + expf(-gg.x)); b *= 1.0f / (1.0f + expf(-gg.y));
+              }
+              __nv_bfloat162 o2 = __floats2bfloat162_rn(a, b);
               pk[j >> 1] = *reinterpret_cast<uint32_t*>(&o2);
             }
             *reinterpret_cast<uint4*>(orow + c * 16) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
@@ -622,11 +636,16 @@ extern "C" int rl_attention_prefill_tc_supported(int num_heads, int num_kv_heads
 // (sequence, tile of the sequence), every tile of the step once, in the order the blocks should
 // start in (heaviest first).  The pools must hold finite values
 // everywhere (see the note at the top of this file).
-extern "C" int rl_attention_prefill_tc(const void* q, int ldq, const void* k_pool, const void* v_pool, int num_pages,
-                                       const int* page_table, int max_pages, const int* cu_seqlens,
-                                       const int* seq_slots, const int* kv_lens, int num_seqs, int num_tiles,
-                                       int num_tokens, void* out, int ldo, int num_heads, int num_kv_heads, int head_dim,
-                                       float scale, int window, int* err, const int* tile_order, cudaStream_t stream) {
+// sink != 0: one more term of score 0 in the softmax's denominator.  gate (may be null): bf16 [M, ldg],
+// 16-byte aligned with ldg a multiple of 8; the output is multiplied by sigmoid(gate[m, h*head_dim + i]).
+extern "C" int rl_attention_prefill_tc_gated(const void* q, int ldq, const void* k_pool, const void* v_pool, int num_pages,
+                                             const int* page_table, int max_pages, const int* cu_seqlens,
+                                             const int* seq_slots, const int* kv_lens, int num_seqs, int num_tiles,
+                                             int num_tokens, void* out, int ldo, int num_heads, int num_kv_heads, int head_dim,
+                                             float scale, int window, int* err, const int* tile_order, int sink,
+                                             const void* gate, int ldg, cudaStream_t stream) {
+  RL_REQUIRE(gate == nullptr || (ldg >= num_heads * head_dim && ldg % 8 == 0 && ((uintptr_t)gate & 15) == 0),
+             "rl_attention_prefill_tc: the gate must be 16-byte aligned with a row stride that is a multiple of 8 and holds all heads");
   RL_REQUIRE(rl_attention_prefill_tc_supported(num_heads, num_kv_heads, head_dim),
              "rl_attention_prefill_tc: unsupported shape (heads %d, KV heads %d, head_dim %d): needs head_dim 64 or 128",
              num_heads, num_kv_heads, head_dim);
@@ -656,13 +675,25 @@ extern "C" int rl_attention_prefill_tc(const void* q, int ldq, const void* k_poo
   cudaError_t e = head_dim == 128
       ? rl_launch_pdl(attention_prefill_tc_kernel<128>, dim3(num_heads, num_tiles), dim3(FA_THREADS), (size_t)FaSizes<128>::SMEM, stream,
                       mq, mk, mv, page_table, max_pages, cu_seqlens, seq_slots, kv_lens, num_seqs,
-                      (__nv_bfloat16*)out, ldo, num_heads, num_kv_heads, scale * 1.4426950408889634f, window, err, tile_order)
+                      (__nv_bfloat16*)out, ldo, num_heads, num_kv_heads, scale * 1.4426950408889634f, window, err, tile_order,
+                      sink, (const __nv_bfloat16*)gate, ldg)
       : rl_launch_pdl(attention_prefill_tc_kernel<64>, dim3(num_heads, num_tiles), dim3(FA_THREADS), (size_t)FaSizes<64>::SMEM, stream,
                       mq, mk, mv, page_table, max_pages, cu_seqlens, seq_slots, kv_lens, num_seqs,
-                      (__nv_bfloat16*)out, ldo, num_heads, num_kv_heads, scale * 1.4426950408889634f, window, err, tile_order);
+                      (__nv_bfloat16*)out, ldo, num_heads, num_kv_heads, scale * 1.4426950408889634f, window, err, tile_order,
+                      sink, (const __nv_bfloat16*)gate, ldg);
   if (e != cudaSuccess) {
     rl_set_error("rl_attention_prefill_tc: launch failed: %s", cudaGetErrorString(e));
     return RL_ERR_CUDA;
   }
   return RL_OK;
+}
+
+extern "C" int rl_attention_prefill_tc(const void* q, int ldq, const void* k_pool, const void* v_pool, int num_pages,
+                                       const int* page_table, int max_pages, const int* cu_seqlens,
+                                       const int* seq_slots, const int* kv_lens, int num_seqs, int num_tiles,
+                                       int num_tokens, void* out, int ldo, int num_heads, int num_kv_heads, int head_dim,
+                                       float scale, int window, int* err, const int* tile_order, cudaStream_t stream) {
+  return rl_attention_prefill_tc_gated(q, ldq, k_pool, v_pool, num_pages, page_table, max_pages, cu_seqlens, seq_slots, kv_lens,
+                                       num_seqs, num_tiles, num_tokens, out, ldo, num_heads, num_kv_heads, head_dim, scale, window,
+                                       err, tile_order, 0, nullptr, 0, stream);
 }

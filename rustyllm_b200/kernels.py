@@ -63,6 +63,15 @@ _SIGNATURES = {
                              _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "rl_attention_decode": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
                             _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void_p],
+    "rl_attention_decode_gated": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                                  _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
+                                  _c_int, _c_void_p, _c_int, _c_void_p],
+    "rl_attention_prefill_gated": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                                   _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
+                                   _c_int, _c_void_p, _c_int, _c_void_p],
+    "rl_attention_prefill_tc_gated": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
+                                      _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float,
+                                      _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p],
     "rl_attention_decode_plan": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "rl_attention_decode_order": [_c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p],
     "rl_attention_decode_places": [_c_int],
@@ -563,6 +572,18 @@ def gemm_tc_qkv_rope(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, bias: 
     _count()
 
 
+def _gate_args(gate: Optional[torch.Tensor], rows: int, width: int, align: int):
+    """Pointer and row stride of an output gate [rows, width] bf16 (a view is fine), or (None, 0)."""
+    if gate is None:
+        return None, 0
+    _need(gate, "gate", torch.bfloat16, contiguous=False)
+    assert gate.shape == (rows, width) and gate.stride(1) == 1
+    ldg = gate.stride(0) if rows > 1 else max(gate.stride(0), width)
+    if gate.data_ptr() % align or (ldg * 2) % align:
+        raise KernelError(f"the gate must be {align}-byte aligned, rows included")
+    return gate.data_ptr(), ldg
+
+
 # ----------------------------------------------------------------------------- decode attention
 _num_sms = {}
 
@@ -716,7 +737,8 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
                      seq_slots: torch.Tensor, kv_lens: torch.Tensor, out: torch.Tensor, num_heads: int,
                      num_kv_heads: int, head_dim: int, scale: float, window: int = 0,
                      num_splits: Optional[int] = None, scratch: Optional[torch.Tensor] = None,
-                     plan: Optional[torch.Tensor] = None, cluster: bool = False) -> None:
+                     plan: Optional[torch.Tensor] = None, cluster: bool = False, sink: bool = False,
+                     gate: Optional[torch.Tensor] = None) -> None:
     """One token per sequence over the bf16 cache, split over the context (tensor cores).
     q: [B, >= H*hd] bf16 (a view into the qkv buffer is fine); out: [B, H*hd] bf16.
     ``num_splits``: chunks per sequence; with a ``plan`` (from ``decode_plan`` with the
@@ -744,10 +766,12 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
         _need(plan, "plan", torch.int32)
         assert plan.numel() >= 4 * B * num_splits + 2 * B
     ldq = q.stride(0) if B > 1 else max(q.stride(0), num_heads * head_dim)
-    _check(library().rl_attention_decode(
+    gptr, ldg = _gate_args(gate, B, num_heads * head_dim, 2)
+    _check(library().rl_attention_decode_gated(
         q.data_ptr(), ldq, k_pool.data_ptr(), v_pool.data_ptr(), page_table.data_ptr(), page_table.shape[1],
         seq_slots.data_ptr(), kv_lens.data_ptr(), out.data_ptr(), out.stride(0), _ptr(scratch), _ptr(plan), B,
-        num_heads, num_kv_heads, head_dim, float(scale), int(window), int(num_splits), _stream()), "rl_attention_decode")
+        num_heads, num_kv_heads, head_dim, float(scale), int(window), int(num_splits), int(bool(sink)), gptr, ldg,
+        _stream()), "rl_attention_decode")
     _count(2 if num_splits > 1 and not cluster else 1)
 
 
@@ -762,7 +786,7 @@ def attention_prefill_supported(dtype: torch.dtype, num_heads: int, num_kv_heads
 def attention_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
                       cu_seqlens: torch.Tensor, seq_slots: torch.Tensor, kv_lens: torch.Tensor, q_lens,
                       out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                      window: int = 0) -> None:
+                      window: int = 0, sink: bool = False, gate: Optional[torch.Tensor] = None) -> None:
     """Causal attention of packed query tokens over the bf16 cache (tensor cores).
     q: [M, >= H*hd] bf16; cu_seqlens [B+1], seq_slots [B], kv_lens [B] on the device;
     q_lens: host list of tokens per sequence; out: [M, H*hd] bf16."""
@@ -775,10 +799,12 @@ def attention_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
     assert q.shape[0] == sum(q_lens) and q.stride(1) == 1
     tiles = sum(-(-n // PREFILL_QTILE) for n in q_lens)
     ldq = q.stride(0) if q.shape[0] > 1 else max(q.stride(0), num_heads * head_dim)
-    _check(library().rl_attention_prefill(
+    gptr, ldg = _gate_args(gate, q.shape[0], num_heads * head_dim, 4)
+    _check(library().rl_attention_prefill_gated(
         q.data_ptr(), ldq, k_pool.data_ptr(), v_pool.data_ptr(), page_table.data_ptr(), page_table.shape[1],
         cu_seqlens.data_ptr(), seq_slots.data_ptr(), kv_lens.data_ptr(), B, tiles, out.data_ptr(), out.stride(0),
-        num_heads, num_kv_heads, head_dim, float(scale), int(window), _stream()), "rl_attention_prefill")
+        num_heads, num_kv_heads, head_dim, float(scale), int(window), int(bool(sink)), gptr, ldg, _stream()),
+        "rl_attention_prefill")
     _count()
 
 
@@ -806,7 +832,8 @@ def attention_prefill_tc_supported(dtype: torch.dtype, num_heads: int, num_kv_he
 def attention_prefill_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
                          cu_seqlens: torch.Tensor, seq_slots: torch.Tensor, kv_lens: torch.Tensor, q_lens,
                          out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                         window: int = 0, tile_order: Optional[torch.Tensor] = None) -> None:
+                         window: int = 0, tile_order: Optional[torch.Tensor] = None, sink: bool = False,
+                         gate: Optional[torch.Tensor] = None) -> None:
     """The same as ``attention_prefill`` on tcgen05 tensor cores (head size 64 or 128).  The cache
     pools must hold finite values everywhere (the cache zero-fills them when it allocates them).
     ``tile_order``: what ``prefill_tile_order`` made for this step (the blocks then start heaviest first)."""
@@ -822,11 +849,12 @@ def attention_prefill_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
         _need(tile_order, "tile_order", torch.int32)
         assert tile_order.numel() == 2 * tiles
     ldq = q.stride(0) if q.shape[0] > 1 else max(q.stride(0), num_heads * head_dim)
-    _check(library().rl_attention_prefill_tc(
+    gptr, ldg = _gate_args(gate, q.shape[0], num_heads * head_dim, 16)
+    _check(library().rl_attention_prefill_tc_gated(
         q.data_ptr(), ldq, k_pool.data_ptr(), v_pool.data_ptr(), k_pool.shape[0], page_table.data_ptr(),
         page_table.shape[1], cu_seqlens.data_ptr(), seq_slots.data_ptr(), kv_lens.data_ptr(), B, tiles, q.shape[0],
         out.data_ptr(), out.stride(0), num_heads, num_kv_heads, head_dim, float(scale), int(window),
-        _tc_error_word(q.device).data_ptr(), _ptr(tile_order), _stream()), "rl_attention_prefill_tc")
+        _tc_error_word(q.device).data_ptr(), _ptr(tile_order), int(bool(sink)), gptr, ldg, _stream()), "rl_attention_prefill_tc")
     _count()
 
 
@@ -841,7 +869,7 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
     key heads (``value_dim``) run on the any-shape kernel; the tensor-core kernels take
     one width for both.  ``sink``: one more term of score 0 in the softmax's denominator.
     ``gate`` [M, H*vd]: the output is multiplied by sigmoid(gate)."""
-    if (value_dim is not None and value_dim != head_dim) or sink or gate is not None:
+    if value_dim is not None and value_dim != head_dim:
         attention_simt(q, k_pool, v_pool, page_table, step.slot_of_token, step.positions, out,
                        num_heads, num_kv_heads, head_dim, scale, window, value_dim=value_dim, sink=sink, gate=gate)
         return
@@ -860,7 +888,7 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
                     order = derived[("decode_order", int(window))] = decode_order(step.seq_slots, step.kv_lens, window)
             attention_decode(q, k_pool, v_pool, page_table, step.seq_slots, step.kv_lens, out,
                              num_heads, num_kv_heads, head_dim, scale, window, num_splits=cluster, plan=order,
-                             cluster=cluster > 1)
+                             cluster=cluster > 1, sink=sink, gate=gate)
             return
         plan = None
         derived = getattr(step, "derived", None)     # what layers of one step share
@@ -870,10 +898,11 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
             if plan is None:
                 plan = derived[key] = decode_plan(step.seq_slots, step.kv_lens, window, splits)
         attention_decode(q, k_pool, v_pool, page_table, step.seq_slots, step.kv_lens, out,
-                         num_heads, num_kv_heads, head_dim, scale, window, num_splits=splits, plan=plan)
+                         num_heads, num_kv_heads, head_dim, scale, window, num_splits=splits, plan=plan, sink=sink, gate=gate)
         return
     if not step.is_decode and attention_prefill_tc_supported(q.dtype, num_heads, num_kv_heads, head_dim) \
-            and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0:
+            and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 \
+            and (gate is None or (gate.data_ptr() % 16 == 0 and gate.stride(0) % 8 == 0)):
         order = None
         derived = getattr(step, "derived", None)
         if derived is not None and len(step.q_lens) > 1:     # one sequence: the kernel's own reverse order is the heaviest first
@@ -881,14 +910,16 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
             if order is None:
                 order = derived["prefill_tile_order"] = prefill_tile_order(step.q_lens, step.kv_lens_host, q.device)
         attention_prefill_tc(q, k_pool, v_pool, page_table, step.cu_seqlens, step.seq_slots, step.kv_lens,
-                             step.q_lens, out, num_heads, num_kv_heads, head_dim, scale, window, tile_order=order)
+                             step.q_lens, out, num_heads, num_kv_heads, head_dim, scale, window, tile_order=order,
+                             sink=sink, gate=gate)
         return
-    if not step.is_decode and attention_prefill_supported(q.dtype, num_heads, num_kv_heads, head_dim):
+    if not step.is_decode and attention_prefill_supported(q.dtype, num_heads, num_kv_heads, head_dim) \
+            and (gate is None or (gate.data_ptr() % 4 == 0 and gate.stride(0) % 2 == 0)):
         attention_prefill(q, k_pool, v_pool, page_table, step.cu_seqlens, step.seq_slots, step.kv_lens,
-                          step.q_lens, out, num_heads, num_kv_heads, head_dim, scale, window)
+                          step.q_lens, out, num_heads, num_kv_heads, head_dim, scale, window, sink=sink, gate=gate)
         return
     attention_simt(q, k_pool, v_pool, page_table, step.slot_of_token, step.positions, out,
-                   num_heads, num_kv_heads, head_dim, scale, window)
+                   num_heads, num_kv_heads, head_dim, scale, window, sink=sink, gate=gate)
 
 
 from .sampling.config import MAX_TOP_K  # noqa: E402  (one definition, host side)

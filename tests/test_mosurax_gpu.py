@@ -79,7 +79,7 @@ def close(got, ref, dtype, cfg, what):
 
 
 # =========================================================================== mechanisms alone
-def _attention_through_cache(dtype, H, G, hd, vd, window, scale, q, k, v, portions, sink=True, gate=None):
+def _attention_through_cache(dtype, H, G, hd, vd, window, scale, q, k, v, portions, sink=True, gate=None, mma_prefill=False):
     """q [n, H*hd], k [n, G*hd], v [n, G*vd] (float64, one sequence) fed in ``portions`` through the cache
     write and the attention dispatcher, as a mixer does it; returns [n, H*vd] float64."""
     from rustyllm_b200 import kernels as K
@@ -103,8 +103,13 @@ def _attention_through_cache(dtype, H, G, hd, vd, window, scale, q, k, v, portio
         K.rope_kv_write(qkv, st.positions, st.slot_of_token, group.page_table, inv_freq, H, G, hd, 0, False,
                         group.k_pool(layer), group.v_pool(layer), value_dim=vd)
         out = torch.empty((cnt, H * vd), dtype=tdt, device=DEV)
-        K.attention(qkv, group.k_pool(layer), group.v_pool(layer), group.page_table, st, out, H, G, hd, scale,
-                    window or 0, value_dim=vd, sink=sink, gate=qkv[:, (H + G) * hd + G * vd:] if gate is not None else None)
+        if mma_prefill and cnt > 1:        # the mma.sync prompt kernel, which the dispatcher takes where TMA cannot address q
+            K.attention_prefill(qkv, group.k_pool(layer), group.v_pool(layer), group.page_table, st.cu_seqlens, st.seq_slots,
+                                st.kv_lens, st.q_lens, out, H, G, hd, scale, window or 0, sink=sink,
+                                gate=qkv[:, (H + G) * hd + G * vd:] if gate is not None else None)
+        else:
+            K.attention(qkv, group.k_pool(layer), group.v_pool(layer), group.page_table, st, out, H, G, hd, scale,
+                        window or 0, value_dim=vd, sink=sink, gate=qkv[:, (H + G) * hd + G * vd:] if gate is not None else None)
         cache.commit([slot], [cnt])
         outs.append(out.double().cpu())
         at += cnt
@@ -130,6 +135,9 @@ def test_attention_with_sink_window_and_gate_alone(dtype, H, G, hd, vd, window):
     got = _attention_through_cache(dtype, H, G, hd, vd, window, scale, q, k, v, [67, 61] + [1] * 22, gate=gate)
     tol = 2e-5 if dtype == "float32" else 2e-2
     assert (got - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item())
+    if dtype == "bfloat16" and hd == vd and hd in (64, 128):
+        got = _attention_through_cache(dtype, H, G, hd, vd, window, scale, q, k, v, [67, 61, 22], gate=gate, mma_prefill=True)
+        assert (got - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item())
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
