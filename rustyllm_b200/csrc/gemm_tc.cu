@@ -199,6 +199,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int num_splits = (int)cluster_size(), split = (int)cluster_rank();
   const int n0 = (blockIdx.x / num_splits) * BLOCK_N_OUT;   // first weight row (output feature) of this CTA
   const int m0 = blockIdx.y * BT;                           // first token of this CTA
+  int w_row0 = n0;                                          // first row of the weight tile in the weight's tensor map
+  if (fuse.tile_group != nullptr) {
+    // grouped: which of the stacked matrices this token tile meets is written by a kernel in front,
+    // so it is read behind the wait; all CTAs of a cluster share the tile and leave together
+    rl_pdl_wait();
+    const int group = fuse.tile_group[blockIdx.y];
+    if (group < 0) return;
+    w_row0 += group * fuse.group_rows;
+  }
   const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
   const int kb0 = split * kb_per_split;                            // this CTA's part of the K range
   const int num_kb = min(kb_per_split, total_kb - kb0);            // > 0: the host sizes the parts so
@@ -230,7 +239,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       for (int kb = 0; kb < pre; ++kb) {
         const uint32_t fb = smem_u32(&full_bar[kb]);
         mbar_expect_tx(fb, Cfg::STAGE_BYTES);
-        tma_load_2d(smem_u32(tiles + (size_t)kb * Cfg::STAGE_BYTES), &map_w, fb, (kb0 + kb) * BLOCK_K, n0);
+        tma_load_2d(smem_u32(tiles + (size_t)kb * Cfg::STAGE_BYTES), &map_w, fb, (kb0 + kb) * BLOCK_K, w_row0);
       }
       rl_pdl_wait();
       for (int kb = 0; kb < pre; ++kb)
@@ -246,7 +255,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const uint32_t fb = smem_u32(&full_bar[s]);
         mbar_expect_tx(fb, Cfg::STAGE_BYTES);
         uint8_t* st = tiles + (size_t)s * Cfg::STAGE_BYTES;
-        tma_load_2d(smem_u32(st), &map_w, fb, (kb0 + kb) * BLOCK_K, n0);
+        tma_load_2d(smem_u32(st), &map_w, fb, (kb0 + kb) * BLOCK_K, w_row0);
         tma_load_2d(smem_u32(st + BLOCK_N_OUT * BLOCK_K * 2), &map_a, fb, (kb0 + kb) * BLOCK_K, m0);
       }
     }
@@ -804,6 +813,40 @@ extern "C" int rl_gemm_tc(const void* A, const void* W, const float* bias, void*
   fuse.norm_weight = norm_weight; fuse.norm_out = (__nv_bfloat16*)norm_out; fuse.ld_norm = ld_norm;
   fuse.norm_partials = norm_partials;
   return gemm_tc_run(A, W, bias, out, out_mode, M, N, K, lda, ldo, err, force_splits, fuse, stream);
+}
+
+// Grouped product: W is `groups` matrices [N, K] one after another ([groups * N, K]); token tile t (rows
+// t * bt .. of A and of out) multiplies with matrix tile_group[t] (device ints, written by a kernel in front;
+// negative: the tile is skipped and its rows of out stay as they are).  A: [M, K] with M a multiple of the
+// token tile bt (16, 32, 64, 128 or 256), rows ordered by group and padded so that no tile holds two groups.
+// out_mode 0, 1, 2 or 3 as in rl_gemm_tc; no bias, no norm riding along.
+extern "C" int rl_gemm_tc_grouped(const void* A, const void* W, void* out, int out_mode, int M, int N, int K, int lda,
+                                  int ldo, int* err, const int* tile_group, int groups, int bt, cudaStream_t stream) {
+  RL_REQUIRE(rl_gemm_tc_supported(A, W, M, N, K, lda), "rl_gemm_tc_grouped: operands not supported (M=%d N=%d K=%d lda=%d; K and lda "
+             "must be multiples of 8 and the bases 16-byte aligned)", M, N, K, lda);
+  RL_REQUIRE(out_mode >= 0 && out_mode <= 3, "rl_gemm_tc_grouped: unknown output mode %d", out_mode);
+  RL_REQUIRE(out_mode != TC_OUT_SWIGLU || N % 2 == 0, "rl_gemm_tc_grouped: the SwiGLU epilogue needs an even number of weight rows, got %d", N);
+  RL_REQUIRE(ldo >= (out_mode == TC_OUT_SWIGLU ? N / 2 : N) && err != nullptr && tile_group != nullptr && groups > 0,
+             "rl_gemm_tc_grouped: bad output stride, null error word or no groups");
+  RL_REQUIRE((bt == 16 || bt == 32 || bt == 64 || bt == 128 || bt == 256) && M % bt == 0,
+             "rl_gemm_tc_grouped: the token tile must be 16, 32, 64, 128 or 256 and divide M (%d, %d)", bt, M);
+  RL_REQUIRE((long long)groups * N <= 2147483647LL && M / bt <= 65535, "rl_gemm_tc_grouped: too many weight rows or token tiles");
+  TcFuse fuse = {};
+  fuse.tile_group = tile_group; fuse.group_rows = N;
+  fuse.norm_count = 4 * ((N + BLOCK_N_OUT - 1) / BLOCK_N_OUT);
+  const int total_kb = (K + BLOCK_K - 1) / BLOCK_K;
+  CUtensorMap mw, ma;
+  int rc = tc_make_map(&mw, W, groups * N, K, K, BLOCK_N_OUT);
+  if (rc != RL_OK) return rc;
+  rc = tc_make_map(&ma, A, M, K, lda, bt);
+  if (rc != RL_OK) return rc;
+  switch (bt) {
+    case 16: return launch_tc_as<16, false>(mw, ma, nullptr, out, out_mode, M, N, K, ldo, err, 1, total_kb, fuse, stream);
+    case 32: return launch_tc_as<32, false>(mw, ma, nullptr, out, out_mode, M, N, K, ldo, err, 1, total_kb, fuse, stream);
+    case 64: return launch_tc_as<64, false>(mw, ma, nullptr, out, out_mode, M, N, K, ldo, err, 1, total_kb, fuse, stream);
+    case 128: return launch_tc_as<128, false>(mw, ma, nullptr, out, out_mode, M, N, K, ldo, err, 1, total_kb, fuse, stream);
+    default: return launch_tc_as<256, false>(mw, ma, nullptr, out, out_mode, M, N, K, ldo, err, 1, total_kb, fuse, stream);
+  }
 }
 
 // 1 if rl_gemm_tc_qkv_rope takes the shape: head size 128 or 64, the whole head rotated, a step

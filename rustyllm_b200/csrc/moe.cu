@@ -87,10 +87,32 @@ extern "C" int rl_moe_route(const void* x, int ldx, const void* router, const fl
 
 // ------------------------------------------------------------------ gate and up of the chosen experts
 // grid (row blocks of F, M * top); the token's input in shared memory; a warp a row of the expert.
+// 8 consecutive elements of a row times 8 of the input, for rows whose length is a multiple of 8 (bf16: one
+// 16-byte load a lane, so a warp's load instruction covers 512 consecutive bytes of the weight row)
+__device__ __forceinline__ float moe_dot8(const __nv_bfloat16* w, const float* xs) {
+  const uint4 v = *reinterpret_cast<const uint4*>(w);
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+  float acc = 0.f;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 f = __bfloat1622float2(p[k]);
+    acc = fmaf(xs[2 * k], f.x, acc);
+    acc = fmaf(xs[2 * k + 1], f.y, acc);
+  }
+  return acc;
+}
+__device__ __forceinline__ float moe_dot8(const float* w, const float* xs) {
+  float acc = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc = fmaf(xs[k], w[k], acc);
+  return acc;
+}
+
+// interleaved: an expert's rows are (gate_0, up_0, gate_1, up_1, ...) instead of all gate rows, then all up rows
 template <typename T>
 __global__ void __launch_bounds__(MOE_THREADS)
 moe_gate_up_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ wgu, const int* __restrict__ ids,
-                   int d, int F, int top, T* __restrict__ h) {
+                   int d, int F, int top, T* __restrict__ h, int interleaved) {
   extern __shared__ float s_x[];          // [d]
   rl_pdl_trigger();
   rl_pdl_wait();
@@ -102,13 +124,20 @@ moe_gate_up_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ wgu, 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = blockIdx.x * (MOE_THREADS / 32) + warp;
   if (r >= F) return;
-  const T* wg = wgu + ((size_t)e * 2 * F + r) * d;
-  const T* wu = wg + (size_t)F * d;
+  const T* wg = wgu + ((size_t)e * 2 * F + (interleaved ? 2 * r : r)) * d;
+  const T* wu = wg + (size_t)(interleaved ? 1 : F) * d;
   float g = 0.f, u = 0.f;
-  for (int i = lane; i < d; i += 32) {
-    const float xv = s_x[i];
-    g = fmaf(xv, rl_ld(wg + i), g);
-    u = fmaf(xv, rl_ld(wu + i), u);
+  if (d % 8 == 0 && ((uintptr_t)wgu & 15) == 0) {
+    for (int i = 8 * lane; i < d; i += 256) {
+      g += moe_dot8(wg + i, s_x + i);
+      u += moe_dot8(wu + i, s_x + i);
+    }
+  } else {
+    for (int i = lane; i < d; i += 32) {
+      const float xv = s_x[i];
+      g = fmaf(xv, rl_ld(wg + i), g);
+      u = fmaf(xv, rl_ld(wu + i), u);
+    }
   }
   g = rl_warp_sum(g);
   u = rl_warp_sum(u);
@@ -133,18 +162,27 @@ moe_down_kernel(const T* __restrict__ h, const T* __restrict__ wd, const int* __
     const T* w = wd + ((size_t)e * d + r) * F;
     const T* hr = h + ((size_t)m * top + c) * F;
     float part = 0.f;
-    for (int i = lane; i < F; i += 32) part = fmaf(rl_ld(hr + i), rl_ld(w + i), part);
+    if (F % 8 == 0 && ((uintptr_t)wd & 15) == 0 && ((uintptr_t)h & 15) == 0) {
+      for (int i = 8 * lane; i < F; i += 256) {
+        float hs[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) hs[k] = rl_ld(hr + i + k);
+        part += moe_dot8(w + i, hs);
+      }
+    } else {
+      for (int i = lane; i < F; i += 32) part = fmaf(rl_ld(hr + i), rl_ld(w + i), part);
+    }
     part = rl_warp_sum(part);
     y = fmaf(weights[(size_t)m * top + c], part, y);
   }
   if (lane == 0) residual[(size_t)m * d + r] += y;
 }
 
-// x [M, ldx]; gate_up [E, 2, F, d]; down [E, d, F]; ids, weights [M, top] (from rl_moe_route);
+// x [M, ldx]; gate_up [E, 2, F, d], or with `interleaved` [E, F, 2, d] (gate_r, up_r in turn); down [E, d, F]; ids, weights [M, top] (from rl_moe_route);
 // h [M * top, F] scratch in the same dtype; residual [M, d] float, added into.
 extern "C" int rl_moe_experts(const void* x, int ldx, const void* gate_up, const void* down, int dtype, const int* ids,
                               const float* weights, int num_tokens, int hidden, int expert_ff, int num_experts, int top,
-                              void* h, float* residual, cudaStream_t stream) {
+                              int interleaved, void* h, float* residual, cudaStream_t stream) {
   RL_REQUIRE(num_tokens >= 0 && hidden > 0 && expert_ff > 0 && num_experts > 0 && top > 0,
              "rl_moe_experts: bad sizes M=%d d=%d F=%d E=%d top=%d", num_tokens, hidden, expert_ff, num_experts, top);
   RL_REQUIRE((long long)num_tokens * top <= 65535LL * 1024, "rl_moe_experts: too many (token, choice) pairs for one launch");
@@ -159,12 +197,12 @@ extern "C" int rl_moe_experts(const void* x, int ldx, const void* gate_up, const
     const size_t smem = (size_t)hidden * sizeof(float);
     if (dtype == RL_F32) {
       rl_launch_pdl(moe_gate_up_kernel<float>, g1, MOE_THREADS, smem, stream, (const float*)x + (size_t)m0 * ldx, ldx, (const float*)gate_up,
-                    ids + p0, hidden, expert_ff, top, (float*)h + (size_t)p0 * expert_ff);
+                    ids + p0, hidden, expert_ff, top, (float*)h + (size_t)p0 * expert_ff, interleaved);
       rl_launch_pdl(moe_down_kernel<float>, g2, MOE_THREADS, 0, stream, (const float*)h + (size_t)p0 * expert_ff, (const float*)down,
                     ids + p0, weights + p0, hidden, expert_ff, top, residual + (size_t)m0 * hidden);
     } else if (dtype == RL_BF16) {
       rl_launch_pdl(moe_gate_up_kernel<__nv_bfloat16>, g1, MOE_THREADS, smem, stream, (const __nv_bfloat16*)x + (size_t)m0 * ldx, ldx,
-                    (const __nv_bfloat16*)gate_up, ids + p0, hidden, expert_ff, top, (__nv_bfloat16*)h + (size_t)p0 * expert_ff);
+                    (const __nv_bfloat16*)gate_up, ids + p0, hidden, expert_ff, top, (__nv_bfloat16*)h + (size_t)p0 * expert_ff, interleaved);
       rl_launch_pdl(moe_down_kernel<__nv_bfloat16>, g2, MOE_THREADS, 0, stream, (const __nv_bfloat16*)h + (size_t)p0 * expert_ff,
                     (const __nv_bfloat16*)down, ids + p0, weights + p0, hidden, expert_ff, top, residual + (size_t)m0 * hidden);
     } else {
@@ -172,5 +210,100 @@ extern "C" int rl_moe_experts(const void* x, int ldx, const void* gate_up, const
     }
     RL_LAUNCH_CHECK("rl_moe_experts");
   }
+  return RL_OK;
+}
+
+// ------------------------------------------------------------------ the tensor-core way: rows ordered by expert
+// For many tokens the chosen experts run as grouped matrix products (rl_gemm_tc_grouped): the (token, choice)
+// pairs are put in the order of their experts, every expert's rows padded to whole token tiles of `bt` rows, so
+// that a tile meets one expert's matrix.
+//   plan   : row[p] = the pair's row; tile_group[t] = the expert of tile t, or -1 for a tile that holds no pair
+//   gather : xs[row[p], :] = x[p / top, :]
+//   (grouped products: gate and up with the activation in the epilogue, then down, into y [rows, d] float)
+//   combine: residual[m, :] += sum_c weights[m, c] * y[row[m * top + c], :]   (choices in their order)
+// Which row a pair gets within its expert depends on timing; no result does: a row of a product depends on that
+// row alone, and the combination walks a token's choices in their order.
+
+// One block.  counts in shared memory; pairs are ranked within their expert by an atomic counter.
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int* __restrict__ ids, int pairs, int E, int bt, int max_tiles, int* __restrict__ row,
+                int* __restrict__ tile_group) {
+  extern __shared__ int s_plan[];          // [E] counts, then [E] first rows
+  int* s_count = s_plan;
+  int* s_first = s_plan + E;
+  rl_pdl_trigger();
+  rl_pdl_wait();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) s_count[e] = 0;
+  for (int t = threadIdx.x; t < max_tiles; t += blockDim.x) tile_group[t] = -1;
+  __syncthreads();
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) row[p] = atomicAdd(&s_count[ids[p]], 1);   // rank within the expert
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int at = 0;
+    for (int e = 0; e < E; ++e) {
+      s_first[e] = at;
+      at += (s_count[e] + bt - 1) / bt * bt;
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    const int t0 = s_first[e] / bt, nt = (s_count[e] + bt - 1) / bt;
+    for (int t = 0; t < nt; ++t)
+      if (t0 + t < max_tiles) tile_group[t0 + t] = e;
+  }
+  for (int p = threadIdx.x; p < pairs; p += blockDim.x) row[p] += s_first[ids[p]];
+}
+
+__global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, int ldx, const int* __restrict__ row, int top, int d,
+                                  __nv_bfloat16* __restrict__ xs) {
+  rl_pdl_trigger();
+  rl_pdl_wait();
+  const int p = blockIdx.x;
+  const __nv_bfloat16* src = x + (size_t)(p / top) * ldx;
+  __nv_bfloat16* dst = xs + (size_t)row[p] * d;
+  for (int i = threadIdx.x; i < d / 8; i += blockDim.x)          // d is a multiple of 8, rows 16-byte aligned
+    reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+}
+
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ row, const float* __restrict__ weights,
+                                   int top, int d, float* __restrict__ residual) {
+  rl_pdl_trigger();
+  rl_pdl_wait();
+  const int m = blockIdx.x;
+  for (int i = threadIdx.x; i < d; i += blockDim.x) {
+    float acc = 0.f;
+    for (int c = 0; c < top; ++c) acc = fmaf(weights[(size_t)m * top + c], y[(size_t)row[(size_t)m * top + c] * d + i], acc);
+    residual[(size_t)m * d + i] += acc;
+  }
+}
+
+// Rows the ordered layout can need for `pairs` pairs over E experts at a token tile of bt: every expert's rows
+// rounded up to whole tiles.
+extern "C" long long rl_moe_sorted_rows(long long pairs, int num_experts, int bt) {
+  const long long used = pairs < num_experts ? pairs : num_experts;       // experts that can hold a pair
+  return (pairs + used * (bt - 1)) / bt * bt;
+}
+
+extern "C" int rl_moe_plan(const int* ids, int pairs, int num_experts, int bt, int max_tiles, int* row, int* tile_group,
+                           cudaStream_t stream) {
+  RL_REQUIRE(pairs > 0 && num_experts > 0 && num_experts <= 4096 && bt > 0 && max_tiles > 0, "rl_moe_plan: bad sizes");
+  rl_launch_pdl(moe_plan_kernel, 1, 1024, (size_t)2 * num_experts * sizeof(int), stream, ids, pairs, num_experts, bt, max_tiles, row, tile_group);
+  RL_LAUNCH_CHECK("rl_moe_plan");
+  return RL_OK;
+}
+
+extern "C" int rl_moe_gather(const void* x, int ldx, const int* row, int pairs, int top, int hidden, void* xs, cudaStream_t stream) {
+  RL_REQUIRE(pairs > 0 && top > 0 && hidden % 8 == 0 && ldx % 8 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)xs & 15) == 0,
+             "rl_moe_gather: rows must be 16-byte aligned and a multiple of 8 long");
+  rl_launch_pdl(moe_gather_kernel, pairs, 128, 0, stream, (const __nv_bfloat16*)x, ldx, row, top, hidden, (__nv_bfloat16*)xs);
+  RL_LAUNCH_CHECK("rl_moe_gather");
+  return RL_OK;
+}
+
+extern "C" int rl_moe_combine(const float* y, const int* row, const float* weights, int num_tokens, int top, int hidden,
+                              float* residual, cudaStream_t stream) {
+  RL_REQUIRE(num_tokens > 0 && top > 0 && hidden > 0, "rl_moe_combine: bad sizes");
+  rl_launch_pdl(moe_combine_kernel, num_tokens, 256, 0, stream, y, row, weights, top, hidden, residual);
+  RL_LAUNCH_CHECK("rl_moe_combine");
   return RL_OK;
 }

@@ -39,6 +39,11 @@ struct TcFuse {
   int head_dim;                 // 128 (a tile of 128 output columns is one head) or 64 (two heads)
   __nv_bfloat16* k_pool;        // [pages, kv_heads, RL_PAGE, head_dim]; null: keys and values are not stored
   __nv_bfloat16* v_pool;
+  // grouped product (null: none): the weight is `groups` matrices of group_rows x K one after another,
+  // and token tile t (blockIdx.y) multiplies with matrix tile_group[t]; a tile with a negative entry is
+  // not computed.  The table is written by a kernel of the same step.
+  const int* tile_group;
+  int group_rows;
 };
 
 static constexpr int BLOCK_N_OUT = 128;   // weight rows per CTA (MMA M)

@@ -55,7 +55,12 @@ _SIGNATURES = {
     "rl_moe_route": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
                      _c_void_p],
     "rl_moe_experts": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
-                       _c_int, _c_void_p, _c_void_p, _c_void_p],
+                       _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
+    "rl_moe_plan": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
+    "rl_moe_gather": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    "rl_moe_combine": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    "rl_gemm_tc_grouped": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p,
+                           _c_void_p, _c_int, _c_int, _c_void_p],
     "rl_repeat_penalty": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_float, _c_void_p],
     "rl_argmax": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p],
     "rl_sample_temperature": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
@@ -249,22 +254,73 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor
 
 
 def moe_experts(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
-                residual: torch.Tensor) -> None:
+                residual: torch.Tensor, interleaved: bool = False) -> None:
     """residual[m] += sum_c weights[m, c] * down[e] (silu(gate[e] x[m]) * (up[e] x[m])), e = ids[m, c], on the
-    CUDA cores (any sizes, float32 or bfloat16 storage).  gate_up: [E, 2, F, d] (an expert's gate rows, then
-    its up rows), down: [E, d, F]."""
+    CUDA cores (any sizes, float32 or bfloat16 storage): every (token, choice) pair reads its expert's rows,
+    which is what a step of few tokens needs.  gate_up: [E, 2, F, d] (an expert's gate rows, then its up
+    rows) or, ``interleaved``, [E, F, 2, d] (gate_r, up_r in turn); down: [E, d, F]."""
     _need(x, "x", contiguous=False); _need(gate_up, "gate_up", x.dtype); _need(down, "down", x.dtype)
     _need(ids, "ids", torch.int32); _need(weights, "weights", torch.float32); _need(residual, "residual", torch.float32)
     M, d = x.shape
-    E, two, F, d2 = gate_up.shape
+    if interleaved:
+        E, F, two, d2 = gate_up.shape
+    else:
+        E, two, F, d2 = gate_up.shape
     top = ids.shape[1]
     assert two == 2 and d2 == d and down.shape == (E, d, F) and residual.shape == (M, d) and x.stride(1) == 1
     assert ids.shape == (M, top) and weights.shape == (M, top)
     h = torch.empty((M * top, F), dtype=x.dtype, device=x.device)
     _check(library().rl_moe_experts(x.data_ptr(), x.stride(0) if M > 1 else d, gate_up.data_ptr(), down.data_ptr(), _dt(x),
-                                    ids.data_ptr(), weights.data_ptr(), M, d, F, E, top, h.data_ptr(), residual.data_ptr(),
-                                    _stream()), "rl_moe_experts")
+                                    ids.data_ptr(), weights.data_ptr(), M, d, F, E, top, int(bool(interleaved)), h.data_ptr(),
+                                    residual.data_ptr(), _stream()), "rl_moe_experts")
     _count(2)
+
+
+def moe_token_tile(num_tokens: int, top: int, num_experts: int) -> int:
+    """Rows of a token tile for the grouped products: what an expert gets on average, rounded up to a tile the
+    tensor-core product has (16 to 128; padding every expert to whole tiles costs the less the smaller the tile)."""
+    avg = -(-num_tokens * top // num_experts)
+    return 16 if avg <= 16 else 32 if avg <= 32 else 64 if avg <= 64 else 128
+
+
+def moe_experts_grouped_supported(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor) -> bool:
+    """bf16, rows TMA can address (hidden size and expert size multiples of 8, 16-byte aligned bases)."""
+    return (x.dtype == torch.bfloat16 and gate_up.dtype == torch.bfloat16 and down.dtype == torch.bfloat16
+            and x.shape[1] % 8 == 0 and down.shape[2] % 8 == 0 and x.stride(1) == 1 and (x.stride(0) % 8 == 0 or x.shape[0] == 1)
+            and x.data_ptr() % 16 == 0 and gate_up.data_ptr() % 16 == 0 and down.data_ptr() % 16 == 0)
+
+
+def moe_experts_grouped(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+                        residual: torch.Tensor) -> None:
+    """The same sum as ``moe_experts`` on the tensor cores, for steps of many tokens: the (token, choice) pairs
+    are ordered by expert (every expert's rows padded to whole token tiles), gate and up run as one grouped
+    product with the activation in its epilogue, down as a second one, and the choices of a token are added
+    into the residual in their order.  gate_up: [E, F, 2, d] (gate_r, up_r in turn), down: [E, d, F], bf16."""
+    _need(x, "x", torch.bfloat16, contiguous=False); _need(gate_up, "gate_up", torch.bfloat16); _need(down, "down", torch.bfloat16)
+    _need(ids, "ids", torch.int32); _need(weights, "weights", torch.float32); _need(residual, "residual", torch.float32)
+    M, d = x.shape
+    E, F, two, d2 = gate_up.shape
+    top = ids.shape[1]
+    assert two == 2 and d2 == d and down.shape == (E, d, F) and residual.shape == (M, d)
+    pairs = M * top
+    bt = moe_token_tile(M, top, E)
+    rows = (pairs + min(pairs, E) * (bt - 1)) // bt * bt
+    tiles = rows // bt
+    dev = x.device
+    row = torch.empty(pairs, dtype=torch.int32, device=dev)
+    tile_group = torch.empty(tiles, dtype=torch.int32, device=dev)
+    xs = torch.empty((rows, d), dtype=torch.bfloat16, device=dev)
+    h = torch.empty((rows, F), dtype=torch.bfloat16, device=dev)
+    y = torch.empty((rows, d), dtype=torch.float32, device=dev)
+    lib, st, err = library(), _stream(), _tc_error_word(dev).data_ptr()
+    _check(lib.rl_moe_plan(ids.data_ptr(), pairs, E, bt, tiles, row.data_ptr(), tile_group.data_ptr(), st), "rl_moe_plan")
+    _check(lib.rl_moe_gather(x.data_ptr(), x.stride(0) if M > 1 else d, row.data_ptr(), pairs, top, d, xs.data_ptr(), st), "rl_moe_gather")
+    _check(lib.rl_gemm_tc_grouped(xs.data_ptr(), gate_up.data_ptr(), h.data_ptr(), OUT_SWIGLU, rows, 2 * F, d, d, F, err,
+                                  tile_group.data_ptr(), E, bt, st), "rl_gemm_tc_grouped")
+    _check(lib.rl_gemm_tc_grouped(h.data_ptr(), down.data_ptr(), y.data_ptr(), OUT_F32, rows, d, F, F, d, err,
+                                  tile_group.data_ptr(), E, bt, st), "rl_gemm_tc_grouped")
+    _check(lib.rl_moe_combine(y.data_ptr(), row.data_ptr(), weights.data_ptr(), M, top, d, residual.data_ptr(), st), "rl_moe_combine")
+    _count(5)
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, eps: float,

@@ -100,10 +100,11 @@ class DecoderModel:
                    if p not in tensors and not ps.optional_in_file]
         if missing:
             raise KeyError(f"parameters without a tensor: {missing}")
+        self._bound = {}
         for path, (part, name, _) in self._params.items():
             if path in tensors:
                 part.bind({name: tensors[path]})
-        self._bound = dict(tensors)
+                self._bound[path] = getattr(part, name, tensors[path])     # what the part kept (it may have laid it out anew)
 
     def parameter_bytes(self) -> int:
         seen, total = set(), 0

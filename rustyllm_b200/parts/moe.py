@@ -6,8 +6,12 @@ has one, runs for every token and is added.
     C = the ``top`` experts of largest z; w_c = softmax over z restricted to C
     x += sum_{c in C} w_c * Wdown_c (silu(Wgate_c xn) * (Wup_c xn))  [+ shared(xn)]
 
-The experts' matrices are stacked: gate and up as [E, 2, F, d], down as [E, d, F], so one kernel
-indexes any expert.  The shared expert is an ordinary gated feed-forward part of its own sizes.
+The experts' matrices are stacked: gate and up as [E, 2, F, d] (in a bfloat16 run [E, F, 2, d]: a gate row
+and its up row in turn, as the tensor-core product's SwiGLU epilogue wants them), down as [E, d, F], so one
+kernel indexes any expert.  Steps of few tokens run every (token, choice) pair against its expert's rows on
+the CUDA cores (only the chosen experts' weights are read); steps of many tokens order the pairs by expert and
+run two grouped tensor-core products.  The shared expert is an ordinary gated feed-forward part of its own
+sizes.
 """
 from __future__ import annotations
 
@@ -37,6 +41,7 @@ class MoEMLP(FeedForward):
         self.names = names
         self.router_bias = router_bias
         self.shared = build_part("feed_forward", shared, runtime) if shared is not None else None
+        self.interleaved = runtime.compute_dtype == torch.bfloat16
         self.router = self.router_b = self.wgu = self.wdown = None
 
     def sub_parts(self):
@@ -49,13 +54,24 @@ class MoEMLP(FeedForward):
         gu = tuple(ParamSource(p + "." + part + sfx, (F, d)) for p in ex for part in ("gate", "up"))
         specs = {
             "router": ParamSpec((ParamSource(n["router"] + sfx, (E, d)),)),
-            "wgu": ParamSpec(gu),                                                   # [E * 2 * F, d]
+            "wgu": ParamSpec(gu),                                                   # [E * 2 * F, d], see ``bind``
             "wdown": ParamSpec(tuple(ParamSource(p + ".down" + sfx, (d, F)) for p in ex)),   # [E * d, F]
         }
         if self.router_bias:
             specs["router_b"] = ParamSpec((ParamSource(n["router"] + n.get("bias_suffix", ".bias"), (E,)),),
                                           role="vector", init="zeros")
         return specs
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        if self.interleaved and "wgu" in tensors:
+            # [E, 2, F, d] as loaded -> [E, F, 2, d]: a gate row and its up row in turn
+            t = tensors["wgu"]
+            tensors = dict(tensors)
+            tensors["wgu"] = t.view(self.E, 2, self.F, self.d).transpose(1, 2).contiguous().view(self.E * 2 * self.F, self.d)
+        super().bind(tensors)
+
+    # from this many (token, choice) pairs an expert on, the grouped tensor-core products take the step
+    GROUPED_FROM_PAIRS_PER_EXPERT = 8
 
     def forward(self, xn: torch.Tensor, residual: torch.Tensor, step) -> None:
         M = xn.shape[0]
@@ -65,7 +81,14 @@ class MoEMLP(FeedForward):
         if router.dtype != xn.dtype:
             raise K.KernelError(f"the router's matrix is {router.dtype} in a {xn.dtype} run")
         K.moe_route(xn, router, self.router_b, self.top, ids, weights)
-        K.moe_experts(xn, self.wgu.view(self.E, 2, self.F, self.d), self.wdown.view(self.E, self.d, self.F),
-                      ids, weights, residual)
+        wd = self.wdown.view(self.E, self.d, self.F)
+        if self.interleaved:
+            wgu = self.wgu.view(self.E, self.F, 2, self.d)
+            if M * self.top >= self.GROUPED_FROM_PAIRS_PER_EXPERT * self.E and K.moe_experts_grouped_supported(xn, wgu, wd):
+                K.moe_experts_grouped(xn, wgu, wd, ids, weights, residual)
+            else:
+                K.moe_experts(xn, wgu, wd, ids, weights, residual, interleaved=True)
+        else:
+            K.moe_experts(xn, self.wgu.view(self.E, 2, self.F, self.d), wd, ids, weights, residual)
         if self.shared is not None:
             self.shared.forward(xn, residual, step)

@@ -201,7 +201,11 @@ def test_router_and_experts_alone(dtype, E, top, d, F):
     K.moe_route(x.to(tdt).to(DEV), wr.to(tdt).to(DEV), b.float().to(DEV), top, ids, wts)
     res0 = rnd(M, d)
     res = res0.float().to(DEV)
-    K.moe_experts(x.to(tdt).to(DEV), torch.stack([wg, wu], dim=1).to(tdt).to(DEV).contiguous(), wd.to(tdt).to(DEV), ids, wts, res)
+    if dtype == "float32":
+        K.moe_experts(x.to(tdt).to(DEV), torch.stack([wg, wu], dim=1).to(tdt).to(DEV).contiguous(), wd.to(tdt).to(DEV), ids, wts, res)
+    else:       # a bfloat16 run keeps a gate row and its up row in turn
+        K.moe_experts(x.to(tdt).to(DEV), torch.stack([wg, wu], dim=2).to(tdt).to(DEV).contiguous(), wd.to(tdt).to(DEV), ids, wts, res,
+                      interleaved=True)
     for m in range(M):
         chosen, weights = P.route(wr @ x[m] + b, top)
         assert ids[m].tolist() == chosen, m
@@ -209,6 +213,44 @@ def test_router_and_experts_alone(dtype, E, top, d, F):
         y = sum(w_ * P.gated_ff(x[m:m + 1], wg[e], wu[e], wd[e])[0] for e, w_ in zip(chosen, weights))
         tol = 2e-5 if dtype == "float32" else 2e-2
         assert (res[m].double().cpu() - res0[m] - y).abs().max().item() <= tol * max(1.0, y.abs().max().item()), m
+
+
+@pytest.mark.parametrize("E,top,d,F,M", [(5, 2, 64, 24, 300), (3, 3, 48, 16, 77), (4, 1, 128, 40, 513), (12, 4, 96, 72, 1000),
+                                          (6, 2, 256, 136, 2100)])
+def test_experts_as_grouped_tensor_core_products(E, top, d, F, M):
+    """Many tokens: the pairs ordered by expert, two grouped products.  Routing is skewed (one expert takes
+    most tokens, one may take none), so tiles of every fill occur."""
+    from rustyllm_b200 import kernels as K
+    g = torch.Generator().manual_seed(E * 7 + M)
+    rnd = lambda *s: torch.randn(*s, generator=g).to(torch.bfloat16).double()
+    x = rnd(M, d)
+    wg, wu, wd = (t.to(torch.bfloat16).double() for t in (rnd(E, F, d) / math.sqrt(d), rnd(E, F, d) / math.sqrt(d), rnd(E, d, F) / math.sqrt(F)))
+    bias = torch.zeros(E, dtype=torch.float64)
+    bias[0], bias[-1] = 3.0, -30.0 if E > top else 0.0
+    wr = (rnd(E, d) / math.sqrt(d)).to(torch.bfloat16).double()
+    ids = torch.empty((M, top), dtype=torch.int32, device=DEV)
+    wts = torch.empty((M, top), dtype=torch.float32, device=DEV)
+    xb = x.to(torch.bfloat16).to(DEV)
+    K.moe_route(xb, wr.to(torch.bfloat16).to(DEV), bias.float().to(DEV), top, ids, wts)
+    res = torch.zeros((M, d), dtype=torch.float32, device=DEV)
+    gu = torch.stack([wg, wu], dim=2).to(torch.bfloat16).to(DEV).contiguous()          # [E, F, 2, d]
+    assert K.moe_experts_grouped_supported(xb, gu, wd.to(torch.bfloat16).to(DEV))
+    K.moe_experts_grouped(xb, gu, wd.to(torch.bfloat16).to(DEV), ids, wts, res)
+    K.check_device_errors()
+    same = torch.zeros((M, d), dtype=torch.float32, device=DEV)
+    K.moe_experts(xb, gu, wd.to(torch.bfloat16).to(DEV), ids, wts, same, interleaved=True)
+    ids_h, wts_h = ids.cpu(), wts.double().cpu()
+    counts = torch.bincount(ids_h.flatten().long(), minlength=E)
+    assert E == top or counts.max().item() > 2 * counts.min().item()
+    ref = torch.zeros(M, d, dtype=torch.float64)
+    for e in range(E):
+        for c in range(top):
+            rows = (ids_h[:, c] == e).nonzero().flatten()
+            if rows.numel():
+                ref[rows] += wts_h[rows, c:c + 1] * P.gated_ff(x[rows], wg[e], wu[e], wd[e])
+    scale = ref.abs().max().item()
+    assert (res.double().cpu() - ref).abs().max().item() <= 2e-2 * scale
+    assert (same.double().cpu() - ref).abs().max().item() <= 2e-2 * scale
 
 
 def test_embedding_with_positions_pass_entry_soft_cap_and_gate_alone():
