@@ -119,7 +119,15 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true", help="only the batch given (no batch 1 / 64 points)")
     ap.add_argument("--skip-cpu-baseline", action="store_true", help="do not time the CPU baseline (vs_baseline stays null)")
+    ap.add_argument("--designs", action="store_true",
+                    help="instead of the headline workload: prompt and single-token throughput of the Mosurax design beside "
+                         "the Llama decoder at equal layer sizes (rustyllm_b200/bench_designs.py), a JSON line a model")
     args = ap.parse_args()
+
+    if args.designs:
+        from rustyllm_b200 import bench_designs
+        bench_designs.run(sorted(bench_designs.SIZES), steps=args.steps if args.steps != 64 else 32, warmup=max(args.warmup if args.warmup != 24 else 8, 3))
+        return 0
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

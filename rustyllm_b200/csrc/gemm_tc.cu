@@ -428,7 +428,11 @@ __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_a,
                           const __grid_constant__ CUtensorMap map_a_tail, const float* __restrict__ bias,
                           void* __restrict__ out, int out_mode, int M, int N, int K,
-                          int ldo, int* __restrict__ err, int tiles_m, int num_tiles, const TcTail tail) {
+                          int ldo, int* __restrict__ err, int tiles_m, int num_tiles, const TcTail tail,
+                          const int* __restrict__ tile_group, int group_rows) {
+  // tile_group (null: none): the weight is stacked matrices of group_rows rows, and the token tile of BT rows at
+  // m0 multiplies with matrix tile_group[m0 / BT]; negative: the tile is skipped by every role alike.  The table
+  // is written by a kernel in front, so each role reads it behind its wait.
   using Cfg = TcConfig<BT>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -471,9 +475,16 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
       // ---------------- producer ----------------
       int it = 0;                                   // k-blocks issued so far, over all tiles
       bool waited = false, ok = true;
+      if (tile_group != nullptr) { rl_pdl_wait(); waited = true; }
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const TcTileAt at = tc_tile_at(tile, tiles_m, BT, tail);
-        const int n0 = at.n0, m0 = at.m0;
+        int n0 = at.n0;
+        const int m0 = at.m0;
+        if (tile_group != nullptr) {
+          const int group = tile_group[m0 / BT];
+          if (group < 0) continue;
+          n0 += group * group_rows;
+        }
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % Cfg::STAGES;
           const uint32_t phase = (it / Cfg::STAGES) & 1;
@@ -498,8 +509,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
       // ---------------- MMA issuer ----------------
       int it = 0, t = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++t) {
-        const uint32_t idesc = make_idesc(BLOCK_N_OUT, tc_tile_at(tile, tiles_m, BT, tail).bt);
+      if (tile_group != nullptr) rl_pdl_wait();
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const TcTileAt mat = tc_tile_at(tile, tiles_m, BT, tail);
+        if (tile_group != nullptr && tile_group[mat.m0 / BT] < 0) continue;
+        const uint32_t idesc = make_idesc(BLOCK_N_OUT, mat.bt);
         const int buf = t & 1;
         const uint32_t acc_phase = (t >> 1) & 1;
         if (t >= 2 && !mbar_wait(smem_u32(&acc_empty[buf]), acc_phase ^ 1, abort_flag)) {   // epilogue done with this accumulator
@@ -527,6 +541,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
           umma_commit(smem_u32(&empty_bar[s]));
         }
         if (ok) umma_commit(smem_u32(&acc_full[buf]));
+        ++t;
       }
     }
   } else {
@@ -534,10 +549,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
     rl_pdl_wait();
     const int quarter = warp & 3;
     int t = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++t) {
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x) {
+      const TcTileAt at = tc_tile_at(tile, tiles_m, BT, tail);
+      if (tile_group != nullptr && tile_group[at.m0 / BT] < 0) continue;
       const int buf = t & 1;
       const uint32_t acc_phase = (t >> 1) & 1;
-      const TcTileAt at = tc_tile_at(tile, tiles_m, BT, tail);
       if (!mbar_wait(smem_u32(&acc_full[buf]), acc_phase, abort_flag)) {
         if (!*abort_flag) { *abort_flag = 1; atomicExch(err, 3); }
         break;
@@ -548,6 +564,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&acc_empty[buf]));    // this warp has read the accumulator
+      ++t;
     }
   }
   tc_fence_before();
@@ -558,7 +575,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_w, const __gri
 
 template <int BT>
 static int launch_tc_persistent(const CUtensorMap& mw, const CUtensorMap& ma, const void* A, int lda, const float* bias,
-                                void* out, int out_mode, int M, int N, int K, int ldo, int* err, cudaStream_t stream) {
+                                void* out, int out_mode, int M, int N, int K, int ldo, int* err, cudaStream_t stream,
+                                const int* tile_group = nullptr, int group_rows = 0) {
   using Cfg = TcConfig<BT>;
   static bool configured = false;
   if (!configured) {
@@ -575,7 +593,7 @@ static int launch_tc_persistent(const CUtensorMap& mw, const CUtensorMap& ma, co
   TcTail tail = {total, BT, 0, 0, 0, 1};
   int num_tiles = total;
   const int full = (total / num_sms) * num_sms;
-  if (full < total) {
+  if (full < total && tile_group == nullptr) {      // grouped: a narrow tile could lie across two groups' rows
     const int n_first = full / tiles_m, t0_first = (full % tiles_m) * BT;
     for (int bt = 64; bt < BT; bt += 16) {
       const int count_first = (M - t0_first + bt - 1) / bt, per_n = (M + bt - 1) / bt;
@@ -594,7 +612,7 @@ static int launch_tc_persistent(const CUtensorMap& mw, const CUtensorMap& ma, co
   }
   const int grid = num_tiles < num_sms ? num_tiles : num_sms;
   cudaError_t e = rl_launch_pdl(gemm_tc_persistent_kernel<BT>, dim3(grid), dim3(TC_THREADS), (size_t)Cfg::SMEM_BYTES, stream,
-                                mw, ma, ma_tail, bias, out, out_mode, M, N, K, ldo, err, tiles_m, num_tiles, tail);
+                                mw, ma, ma_tail, bias, out, out_mode, M, N, K, ldo, err, tiles_m, num_tiles, tail, tile_group, group_rows);
   if (e != cudaSuccess) {
     rl_set_error("rl_gemm_tc: launch of the persistent kernel failed: %s", cudaGetErrorString(e));
     return RL_ERR_CUDA;
@@ -844,8 +862,9 @@ extern "C" int rl_gemm_tc_grouped(const void* A, const void* W, void* out, int o
     case 16: return launch_tc_as<16, false>(mw, ma, nullptr, out, out_mode, M, N, K, ldo, err, 1, total_kb, fuse, stream);
     case 32: return launch_tc_as<32, false>(mw, ma, nullptr, out, out_mode, M, N, K, ldo, err, 1, total_kb, fuse, stream);
     case 64: return launch_tc_as<64, false>(mw, ma, nullptr, out, out_mode, M, N, K, ldo, err, 1, total_kb, fuse, stream);
-    case 128: return launch_tc_as<128, false>(mw, ma, nullptr, out, out_mode, M, N, K, ldo, err, 1, total_kb, fuse, stream);
-    default: return launch_tc_as<256, false>(mw, ma, nullptr, out, out_mode, M, N, K, ldo, err, 1, total_kb, fuse, stream);
+    // many tokens an expert: the persistent kernel (an accumulator drains while the next tile's products run)
+    case 128: return launch_tc_persistent<128>(mw, ma, A, lda, nullptr, out, out_mode, M, N, K, ldo, err, stream, tile_group, N);
+    default: return launch_tc_persistent<256>(mw, ma, A, lda, nullptr, out, out_mode, M, N, K, ldo, err, stream, tile_group, N);
   }
 }
 

@@ -16,21 +16,50 @@
 #define MOE_THREADS 256
 #define MOE_MAX_TOP 32
 
+// 8 consecutive elements of a row times 8 of the input, for rows whose length is a multiple of 8 (bf16: one
+// 16-byte load a lane, so a warp's load instruction covers 512 consecutive bytes of the weight row)
+__device__ __forceinline__ float moe_dot8(const __nv_bfloat16* w, const float* xs) {
+  const uint4 v = *reinterpret_cast<const uint4*>(w);
+  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
+  float acc = 0.f;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float2 f = __bfloat1622float2(p[k]);
+    acc = fmaf(xs[2 * k], f.x, acc);
+    acc = fmaf(xs[2 * k + 1], f.y, acc);
+  }
+  return acc;
+}
+__device__ __forceinline__ float moe_dot8(const float* w, const float* xs) {
+  float acc = 0.f;
+#pragma unroll
+  for (int k = 0; k < 8; ++k) acc = fmaf(xs[k], w[k], acc);
+  return acc;
+}
+
 // ------------------------------------------------------------------ router
 // One block a token; warp w takes experts w, w + 8, ...; then warp 0 selects.
 template <typename T>
 __global__ void __launch_bounds__(MOE_THREADS)
 moe_route_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ wr, const float* __restrict__ bias,
                  int d, int E, int top, int* __restrict__ ids, float* __restrict__ weights) {
-  extern __shared__ float s_logit[];     // [E]
+  extern __shared__ float s_logit[];     // [E], then the token's input [d]
+  float* s_x = s_logit + ((E + 3) & ~3);
   rl_pdl_trigger();
   rl_pdl_wait();
   const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const T* xr = x + (size_t)m * ldx;
+  for (int i = threadIdx.x; i < d; i += MOE_THREADS) s_x[i] = rl_ld(xr + i);
+  __syncthreads();
+  const bool vec = d % 8 == 0 && ((uintptr_t)wr & 15) == 0;
   for (int e = warp; e < E; e += MOE_THREADS / 32) {
     const T* w = wr + (size_t)e * d;
     float part = 0.f;
-    for (int i = lane; i < d; i += 32) part = fmaf(rl_ld(xr + i), rl_ld(w + i), part);
+    if (vec) {
+      for (int i = 8 * lane; i < d; i += 256) part += moe_dot8(w + i, s_x + i);
+    } else {
+      for (int i = lane; i < d; i += 32) part = fmaf(s_x[i], rl_ld(w + i), part);
+    }
     part = rl_warp_sum(part);
     if (lane == 0) s_logit[e] = part + (bias ? bias[e] : 0.f);
   }
@@ -72,7 +101,8 @@ extern "C" int rl_moe_route(const void* x, int ldx, const void* router, const fl
   RL_REQUIRE(top > 0 && top <= num_experts && top <= MOE_MAX_TOP, "rl_moe_route: top %d must lie in [1, min(%d, %d)]", top, num_experts, MOE_MAX_TOP);
   RL_REQUIRE(num_experts <= 8192, "rl_moe_route: at most 8192 experts");
   if (num_tokens == 0) return RL_OK;
-  const size_t smem = (size_t)num_experts * sizeof(float);
+  RL_REQUIRE(hidden + num_experts <= 11000, "rl_moe_route: hidden size plus experts above 11,000");
+  const size_t smem = (size_t)(((num_experts + 3) & ~3) + hidden) * sizeof(float);
   if (dtype == RL_F32)
     rl_launch_pdl(moe_route_kernel<float>, num_tokens, MOE_THREADS, smem, stream, (const float*)x, ldx, (const float*)router, bias,
                   hidden, num_experts, top, ids, weights);
@@ -87,27 +117,6 @@ extern "C" int rl_moe_route(const void* x, int ldx, const void* router, const fl
 
 // ------------------------------------------------------------------ gate and up of the chosen experts
 // grid (row blocks of F, M * top); the token's input in shared memory; a warp a row of the expert.
-// 8 consecutive elements of a row times 8 of the input, for rows whose length is a multiple of 8 (bf16: one
-// 16-byte load a lane, so a warp's load instruction covers 512 consecutive bytes of the weight row)
-__device__ __forceinline__ float moe_dot8(const __nv_bfloat16* w, const float* xs) {
-  const uint4 v = *reinterpret_cast<const uint4*>(w);
-  const __nv_bfloat162* p = reinterpret_cast<const __nv_bfloat162*>(&v);
-  float acc = 0.f;
-#pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    const float2 f = __bfloat1622float2(p[k]);
-    acc = fmaf(xs[2 * k], f.x, acc);
-    acc = fmaf(xs[2 * k + 1], f.y, acc);
-  }
-  return acc;
-}
-__device__ __forceinline__ float moe_dot8(const float* w, const float* xs) {
-  float acc = 0.f;
-#pragma unroll
-  for (int k = 0; k < 8; ++k) acc = fmaf(xs[k], w[k], acc);
-  return acc;
-}
-
 // interleaved: an expert's rows are (gate_0, up_0, gate_1, up_1, ...) instead of all gate rows, then all up rows
 template <typename T>
 __global__ void __launch_bounds__(MOE_THREADS)

@@ -280,7 +280,7 @@ def moe_token_tile(num_tokens: int, top: int, num_experts: int) -> int:
     """Rows of a token tile for the grouped products: what an expert gets on average, rounded up to a tile the
     tensor-core product has (16 to 128; padding every expert to whole tiles costs the less the smaller the tile)."""
     avg = -(-num_tokens * top // num_experts)
-    return 16 if avg <= 16 else 32 if avg <= 32 else 64 if avg <= 64 else 128
+    return 16 if avg <= 16 else 32 if avg <= 32 else 64 if avg <= 64 else 128 if avg < 512 else 256
 
 
 def moe_experts_grouped_supported(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor) -> bool:

@@ -8,10 +8,10 @@ has one, runs for every token and is added.
 
 The experts' matrices are stacked: gate and up as [E, 2, F, d] (in a bfloat16 run [E, F, 2, d]: a gate row
 and its up row in turn, as the tensor-core product's SwiGLU epilogue wants them), down as [E, d, F], so one
-kernel indexes any expert.  Steps of few tokens run every (token, choice) pair against its expert's rows on
-the CUDA cores (only the chosen experts' weights are read); steps of many tokens order the pairs by expert and
-run two grouped tensor-core products.  The shared expert is an ordinary gated feed-forward part of its own
-sizes.
+kernel indexes any expert.  A bfloat16 step orders its (token, choice) pairs by expert and runs two grouped
+tensor-core products (every chosen expert's weights are read once, whatever the number of tokens it got); the
+32-bit path, and shapes the tensor-core product cannot address, run every pair against its expert's rows on the
+CUDA cores.  The shared expert is an ordinary gated feed-forward part of its own sizes.
 """
 from __future__ import annotations
 
@@ -70,8 +70,8 @@ class MoEMLP(FeedForward):
             tensors["wgu"] = t.view(self.E, 2, self.F, self.d).transpose(1, 2).contiguous().view(self.E * 2 * self.F, self.d)
         super().bind(tensors)
 
-    # from this many (token, choice) pairs an expert on, the grouped tensor-core products take the step
-    GROUPED_FROM_PAIRS_PER_EXPERT = 8
+    # False: every step on the per-pair kernels (for measurements and tests)
+    use_grouped = True
 
     def forward(self, xn: torch.Tensor, residual: torch.Tensor, step) -> None:
         M = xn.shape[0]
@@ -84,7 +84,7 @@ class MoEMLP(FeedForward):
         wd = self.wdown.view(self.E, self.d, self.F)
         if self.interleaved:
             wgu = self.wgu.view(self.E, self.F, 2, self.d)
-            if M * self.top >= self.GROUPED_FROM_PAIRS_PER_EXPERT * self.E and K.moe_experts_grouped_supported(xn, wgu, wd):
+            if self.use_grouped and K.moe_experts_grouped_supported(xn, wgu, wd):
                 K.moe_experts_grouped(xn, wgu, wd, ids, weights, residual)
             else:
                 K.moe_experts(xn, wgu, wd, ids, weights, residual, interleaved=True)

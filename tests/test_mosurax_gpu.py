@@ -216,10 +216,11 @@ def test_router_and_experts_alone(dtype, E, top, d, F):
 
 
 @pytest.mark.parametrize("E,top,d,F,M", [(5, 2, 64, 24, 300), (3, 3, 48, 16, 77), (4, 1, 128, 40, 513), (12, 4, 96, 72, 1000),
-                                          (6, 2, 256, 136, 2100)])
+                                          (6, 2, 256, 136, 2100), (5, 2, 64, 24, 1), (16, 3, 128, 64, 8), (4, 2, 128, 256, 4500)])
 def test_experts_as_grouped_tensor_core_products(E, top, d, F, M):
-    """Many tokens: the pairs ordered by expert, two grouped products.  Routing is skewed (one expert takes
-    most tokens, one may take none), so tiles of every fill occur."""
+    """The pairs ordered by expert, two grouped products, from one token to thousands (token tiles of 16 to
+    256 rows; from 128 on the persistent kernel).  Routing is skewed (one expert takes most tokens, one may
+    take none), so tiles of every fill occur."""
     from rustyllm_b200 import kernels as K
     g = torch.Generator().manual_seed(E * 7 + M)
     rnd = lambda *s: torch.randn(*s, generator=g).to(torch.bfloat16).double()
