@@ -4,6 +4,9 @@
     python -m rustyllm_b200.bench_kernels attention-decode --batch 8 --context 800 [--splits 0] [--contexts 1761,1350,159 | --context-range 128,2048]
     python -m rustyllm_b200.bench_kernels attention-prefill --tokens 2048
     python -m rustyllm_b200.bench_kernels rmsnorm | swiglu | rope --m 8
+    python -m rustyllm_b200.bench_kernels moe --m 2048 --experts 16 --top 3 --hidden 2048 --intermediate 2048 [--pairs]
+    (attention-decode and attention-prefill take --sink, --gate and --window W: the softmax's extra term, the
+    output gate and a sliding window, as the Mosurax design's layers use them)
     python -m rustyllm_b200.bench_kernels sample --m 8 --n 128256 [--greedy | --top-k 40 --top-p 0.9 | --top-p 0.9]
 
 Each run launches the kernel ``--reps`` times after ``--warmup`` launches, rotating over
@@ -93,15 +96,19 @@ def attention_decode(a) -> None:
     pools, pt = _cache(a.batch, a.context, G, hd, layers)
     slots = torch.arange(a.batch, dtype=torch.int32, device=DEV)
     kv = torch.tensor(lens, dtype=torch.int32, device=DEV)
-    q = torch.randn(a.batch, (H + 2 * G) * hd, device=DEV).to(BF)
+    q = torch.randn(a.batch, (H + 2 * G) * hd + (H * hd if a.gate else 0), device=DEV).to(BF)
+    gate = q[:, (H + 2 * G) * hd:] if a.gate else None
+    if a.window:
+        kv_bytes = sum(min(n, a.window) for n in lens) * G * hd * 2 * 2
     out = torch.empty(a.batch, H * hd, device=DEV, dtype=BF)
     sp = a.splits or K.decode_splits(a.batch, G)
-    plan = K.decode_plan(slots, kv, 0, sp) if a.batch > 1 and not a.cluster else None    # once a step, as the engine makes it
+    plan = K.decode_plan(slots, kv, a.window, sp) if a.batch > 1 and not a.cluster else None    # once a step, as the engine makes it
     if a.ordered:                            # every sequence whole, the longest first
-        sp, plan = 1, K.decode_order(slots, kv, 0)
+        sp, plan = 1, K.decode_order(slots, kv, a.window)
     us = _time(lambda i: K.attention_decode(q, pools[i % layers][0], pools[i % layers][1], pt, slots, kv, out, H, G, hd,
-                                            1 / math.sqrt(hd), num_splits=sp, plan=plan, cluster=a.cluster), a.warmup, a.reps)
-    print(f"attention_decode B={a.batch} context={a.contexts or a.context_range or a.context} (mean {sum(lens) / len(lens):.0f}) H={H} G={G} hd={hd} splits={sp}{' in order' if a.ordered else ''}: "
+                                            1 / math.sqrt(hd), a.window, num_splits=sp, plan=plan, cluster=a.cluster,
+                                            sink=a.sink, gate=gate), a.warmup, a.reps)
+    print(f"attention_decode{' sink' if a.sink else ''}{' gate' if a.gate else ''}{f' window {a.window}' if a.window else ''} B={a.batch} context={a.contexts or a.context_range or a.context} (mean {sum(lens) / len(lens):.0f}) H={H} G={G} hd={hd} splits={sp}{' in order' if a.ordered else ''}: "
           f"{us:.2f} us, {kv_bytes / us / 1e6:.2f} TB/s of cache")
 
 
@@ -109,16 +116,19 @@ def attention_prefill(a) -> None:
     H, G, hd, T = a.heads, a.kv_heads, a.head_dim, a.tokens
     pools, pt = _cache(1, T, G, hd, 2)
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
-    q = torch.randn(T, (H + 2 * G) * hd, device=DEV).to(BF)
+    q = torch.randn(T, (H + 2 * G) * hd + (H * hd if a.gate else 0), device=DEV).to(BF)
+    gate = q[:, (H + 2 * G) * hd:] if a.gate else None
     out = torch.empty(T, H * hd, device=DEV, dtype=BF)
     tc = not a.mma and K.attention_prefill_tc_supported(BF, H, G, hd)
     fn = K.attention_prefill_tc if tc else K.attention_prefill
     cu, sl, kl = i32([0, T]), i32([0]), i32([T])
-    us = _time(lambda i: fn(q, pools[i % 2][0], pools[i % 2][1], pt, cu, sl, kl, [T], out, H, G, hd, 1 / math.sqrt(hd)),
-               a.warmup, a.reps)
+    us = _time(lambda i: fn(q, pools[i % 2][0], pools[i % 2][1], pt, cu, sl, kl, [T], out, H, G, hd, 1 / math.sqrt(hd), a.window,
+                            sink=a.sink, gate=gate), a.warmup, a.reps)
     K.check_device_errors()
     flops = 2 * 2 * H * hd * (T * (T + 1) / 2)
-    print(f"attention_prefill ({'tcgen05' if tc else 'mma.sync'}) T={T} H={H} G={G} hd={hd}: {us:.2f} us, "
+    if a.window and a.window < T:
+        flops = 2 * 2 * H * hd * (a.window * (a.window + 1) / 2 + (T - a.window) * a.window)
+    print(f"attention_prefill{' sink' if a.sink else ''}{' gate' if a.gate else ''}{f' window {a.window}' if a.window else ''} ({'tcgen05' if tc else 'mma.sync'}) T={T} H={H} G={G} hd={hd}: {us:.2f} us, "
           f"{flops / us / 1e6:.1f} TFLOP/s (causal half counted)")
 
 
@@ -146,6 +156,29 @@ def sample(a) -> None:
           f"{rows * V * 4 * (1 if a.greedy else 2) / us / 1e3:.1f} GB/s of logits read")
 
 
+def moe(a) -> None:
+    """Router + the chosen experts of one layer: ``--m`` tokens, ``--experts``, ``--top``, ``--hidden`` wide,
+    experts ``--intermediate`` wide; the grouped tensor-core way, or with ``--pairs`` the per-pair kernels."""
+    M, E, top, d, F = a.m, a.experts, a.top, a.hidden, a.intermediate
+    copies = max(2, min(4, int(300e6 // (E * 3 * F * d * 2)) + 1))
+    gu = [(torch.randn(E, F, 2, d, device=DEV) * 0.02).to(BF) for _ in range(copies)]
+    wd = [(torch.randn(E, d, F, device=DEV) * 0.02).to(BF) for _ in range(copies)]
+    wr = (torch.randn(E, d, device=DEV) * 0.05).to(BF)
+    x = torch.randn(M, d, device=DEV).to(BF)
+    res = torch.zeros(M, d, device=DEV)
+    ids = torch.empty(M, top, dtype=torch.int32, device=DEV); wts = torch.empty(M, top, device=DEV)
+    K.moe_route(x, wr, None, top, ids, wts)
+    us_r = _time(lambda i: K.moe_route(x, wr, None, top, ids, wts), a.warmup, a.reps)
+    fn = (lambda i: K.moe_experts(x, gu[i % copies], wd[i % copies], ids, wts, res, interleaved=True)) if a.pairs else \
+        (lambda i: K.moe_experts_grouped(x, gu[i % copies], wd[i % copies], ids, wts, res))
+    us = _time(fn, a.warmup, a.reps)
+    K.check_device_errors()
+    used = int(torch.unique(ids).numel())
+    flops, wbytes = 2.0 * M * top * 3 * F * d, used * 3.0 * F * d * 2
+    print(f"moe {'per pair' if a.pairs else 'grouped'} M={M} E={E} top={top} d={d} F={F} (tile {K.moe_token_tile(M, top, E)}, {used} experts used): "
+          f"router {us_r:.2f} us; experts {us:.2f} us, {wbytes / us / 1e6:.2f} TB/s of the used experts' weights, {flops / us / 1e6:.1f} TFLOP/s")
+
+
 def small(a) -> None:
     d, I, H, G, hd, M = a.hidden, a.intermediate, a.heads, a.kv_heads, a.head_dim, a.m
     if a.kernel == "rmsnorm":
@@ -169,7 +202,7 @@ def small(a) -> None:
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="python -m rustyllm_b200.bench_kernels", description=__doc__,
                                 formatter_class=argparse.RawDescriptionHelpFormatter)
-    p.add_argument("kernel", choices=["gemm", "attention-decode", "attention-prefill", "rmsnorm", "swiglu", "rope", "sample"])
+    p.add_argument("kernel", choices=["gemm", "attention-decode", "attention-prefill", "rmsnorm", "swiglu", "rope", "sample", "moe"])
     p.add_argument("--m", type=int, default=8); p.add_argument("--n", type=int, default=4096); p.add_argument("--k", type=int, default=4096)
     p.add_argument("--mode", default="same", choices=["same", "f32", "add", "swiglu"]); p.add_argument("--parts", type=int, default=0)
     p.add_argument("--batch", type=int, default=8); p.add_argument("--context", type=int, default=800)
@@ -185,13 +218,18 @@ def main(argv=None) -> int:
     p.add_argument("--cluster", action="store_true", help="attention-decode: the chunks of a sequence as one thread-block cluster (--splits 2, 4 or 8)")
     p.add_argument("--ordered", action="store_true", help="attention-decode: every sequence whole, the longest first (a plan made once)")
     p.add_argument("--mma", action="store_true", help="attention-prefill: the mma.sync kernel also where tcgen05 applies")
+    p.add_argument("--sink", action="store_true", help="attention: one more term of score 0 in the softmax's denominator")
+    p.add_argument("--gate", action="store_true", help="attention: the output times sigmoid(gate), the gate beside q, k, v")
+    p.add_argument("--window", type=int, default=0, help="attention: sliding window (0: none)")
+    p.add_argument("--experts", type=int, default=16); p.add_argument("--top", type=int, default=3)
+    p.add_argument("--pairs", action="store_true", help="moe: the per-pair CUDA-core kernels instead of the grouped products")
     p.add_argument("--warmup", type=int, default=3); p.add_argument("--reps", type=int, default=20)
     p.add_argument("--graph", action="store_true", help="capture the timed launches in one CUDA graph: kernels that take "
                    "less time than a launch costs the host are then timed back to back")
     a = p.parse_args(argv)
     global GRAPH
     GRAPH = a.graph
-    {"gemm": gemm, "attention-decode": attention_decode, "attention-prefill": attention_prefill, "sample": sample}.get(a.kernel, small)(a)
+    {"gemm": gemm, "attention-decode": attention_decode, "attention-prefill": attention_prefill, "sample": sample, "moe": moe}.get(a.kernel, small)(a)
     return 0
 
 

@@ -95,6 +95,57 @@ moe_route_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ wr, con
   }
 }
 
+// The selection alone, from logits a matrix product has made (many tokens: the router is then one product
+// [M, d] x [d, E] with the bias in its epilogue, and this kernel - a warp a token - picks and weighs).
+__global__ void __launch_bounds__(MOE_THREADS)
+moe_select_kernel(const float* __restrict__ logits, int M, int E, int top, int* __restrict__ ids, float* __restrict__ weights) {
+  rl_pdl_trigger();
+  rl_pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m = blockIdx.x * (MOE_THREADS / 32) + warp;
+  if (m >= M) return;
+  const float* z = logits + (size_t)m * E;
+  float chosen = 0.f, first = 0.f;
+  int chosen_id = 0;
+  unsigned taken_lo = 0;                 // experts this lane has given away already, for E <= 1024: bit j = expert lane + 32 j
+  for (int c = 0; c < top; ++c) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int e = lane, j = 0; e < E; e += 32, ++j) {
+      if (taken_lo >> j & 1u) continue;
+      const float v = z[e];
+      if (v > best) { best = v; at = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+    }
+    if (at == 0x7fffffff) at = 0;
+    if (c == 0) first = best;
+    if (lane == c) { chosen = best; chosen_id = at; }
+    if ((at & 31) == lane) taken_lo |= 1u << (at >> 5);
+  }
+  const float e_c = lane < top ? expf(chosen - first) : 0.f;
+  const float denom = rl_warp_sum(e_c);
+  if (lane < top) {
+    ids[(size_t)m * top + lane] = chosen_id;
+    weights[(size_t)m * top + lane] = e_c / denom;
+  }
+}
+
+extern "C" int rl_moe_select(const float* logits, int num_tokens, int num_experts, int top, int* ids, float* weights,
+                             cudaStream_t stream) {
+  RL_REQUIRE(num_tokens >= 0 && num_experts > 0 && num_experts <= 1024, "rl_moe_select: bad sizes M=%d E=%d (at most 1,024 experts)", num_tokens, num_experts);
+  RL_REQUIRE(top > 0 && top <= num_experts && top <= MOE_MAX_TOP, "rl_moe_select: top %d must lie in [1, min(%d, %d)]", top, num_experts, MOE_MAX_TOP);
+  if (num_tokens == 0) return RL_OK;
+  const int per = MOE_THREADS / 32;
+  rl_launch_pdl(moe_select_kernel, (num_tokens + per - 1) / per, MOE_THREADS, 0, stream, logits, num_tokens, num_experts, top, ids, weights);
+  RL_LAUNCH_CHECK("rl_moe_select");
+  return RL_OK;
+}
+
 extern "C" int rl_moe_route(const void* x, int ldx, const void* router, const float* bias, int dtype, int num_tokens,
                             int hidden, int num_experts, int top, int* ids, float* weights, cudaStream_t stream) {
   RL_REQUIRE(num_tokens >= 0 && hidden > 0 && num_experts > 0, "rl_moe_route: bad sizes M=%d d=%d E=%d", num_tokens, hidden, num_experts);
@@ -279,10 +330,18 @@ __global__ void moe_combine_kernel(const float* __restrict__ y, const int* __res
   rl_pdl_trigger();
   rl_pdl_wait();
   const int m = blockIdx.x;
-  for (int i = threadIdx.x; i < d; i += blockDim.x) {
-    float acc = 0.f;
-    for (int c = 0; c < top; ++c) acc = fmaf(weights[(size_t)m * top + c], y[(size_t)row[(size_t)m * top + c] * d + i], acc);
-    residual[(size_t)m * d + i] += acc;
+  // d is a multiple of 4 and all rows are 16-byte aligned: four columns a thread, the choices' rows read side by side
+  for (int i = 4 * threadIdx.x; i < d; i += 4 * blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int c = 0; c < top; ++c) {
+      const float w = weights[(size_t)m * top + c];
+      const float4 v = __ldcs(reinterpret_cast<const float4*>(y + (size_t)row[(size_t)m * top + c] * d + i));
+      acc.x = fmaf(w, v.x, acc.x); acc.y = fmaf(w, v.y, acc.y); acc.z = fmaf(w, v.z, acc.z); acc.w = fmaf(w, v.w, acc.w);
+    }
+    float4* r = reinterpret_cast<float4*>(residual + (size_t)m * d + i);
+    float4 o = *r;
+    o.x += acc.x; o.y += acc.y; o.z += acc.z; o.w += acc.w;
+    *r = o;
   }
 }
 
@@ -311,8 +370,9 @@ extern "C" int rl_moe_gather(const void* x, int ldx, const int* row, int pairs, 
 
 extern "C" int rl_moe_combine(const float* y, const int* row, const float* weights, int num_tokens, int top, int hidden,
                               float* residual, cudaStream_t stream) {
-  RL_REQUIRE(num_tokens > 0 && top > 0 && hidden > 0, "rl_moe_combine: bad sizes");
-  rl_launch_pdl(moe_combine_kernel, num_tokens, 256, 0, stream, y, row, weights, top, hidden, residual);
+  RL_REQUIRE(num_tokens > 0 && top > 0 && hidden > 0 && hidden % 4 == 0 && ((uintptr_t)y & 15) == 0 && ((uintptr_t)residual & 15) == 0,
+             "rl_moe_combine: bad sizes (the hidden size must be a multiple of 4, the rows 16-byte aligned)");
+  rl_launch_pdl(moe_combine_kernel, num_tokens, hidden >= 2048 ? 256 : 128, 0, stream, y, row, weights, top, hidden, residual);
   RL_LAUNCH_CHECK("rl_moe_combine");
   return RL_OK;
 }

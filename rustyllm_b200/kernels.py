@@ -54,6 +54,7 @@ _SIGNATURES = {
     "rl_sigmoid_gate": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "rl_moe_route": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p,
                      _c_void_p],
+    "rl_moe_select": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
     "rl_moe_experts": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
                        _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
     "rl_moe_plan": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
@@ -253,6 +254,16 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor
     _count()
 
 
+def moe_select(logits: torch.Tensor, top: int, ids: torch.Tensor, weights: torch.Tensor) -> None:
+    """The router's second half alone: from float32 logits [M, E] (bias included) the ``top`` largest a token
+    (ties to the lower index) and the softmax over them, as ``moe_route`` leaves them."""
+    _need(logits, "logits", torch.float32); _need(ids, "ids", torch.int32); _need(weights, "weights", torch.float32)
+    M, E = logits.shape
+    assert ids.shape == (M, top) and weights.shape == (M, top)
+    _check(library().rl_moe_select(logits.data_ptr(), M, E, int(top), ids.data_ptr(), weights.data_ptr(), _stream()), "rl_moe_select")
+    _count()
+
+
 def moe_experts(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
                 residual: torch.Tensor, interleaved: bool = False) -> None:
     """residual[m] += sum_c weights[m, c] * down[e] (silu(gate[e] x[m]) * (up[e] x[m])), e = ids[m, c], on the
@@ -280,7 +291,7 @@ def moe_token_tile(num_tokens: int, top: int, num_experts: int) -> int:
     """Rows of a token tile for the grouped products: what an expert gets on average, rounded up to a tile the
     tensor-core product has (16 to 128; padding every expert to whole tiles costs the less the smaller the tile)."""
     avg = -(-num_tokens * top // num_experts)
-    return 16 if avg <= 16 else 32 if avg <= 32 else 64 if avg <= 64 else 128 if avg < 512 else 256
+    return 16 if avg <= 16 else 32 if avg <= 32 else 64 if avg <= 64 else 128 if avg < 256 else 256
 
 
 def moe_experts_grouped_supported(x: torch.Tensor, gate_up: torch.Tensor, down: torch.Tensor) -> bool:

@@ -22,6 +22,7 @@ import torch
 from .. import kernels as K
 from ..config.spec import ParamSource, ParamSpec, PartSpec
 from .base import FeedForward, Runtime
+from .linear import OUT_F32, linear
 from .registry import build_part, register_feed_forward
 
 
@@ -70,6 +71,9 @@ class MoEMLP(FeedForward):
             tensors["wgu"] = t.view(self.E, 2, self.F, self.d).transpose(1, 2).contiguous().view(self.E * 2 * self.F, self.d)
         super().bind(tensors)
 
+    # from this many tokens on the router's logits are a matrix product and a selection kernel; below, one kernel
+    # that does both a token a block (two launches cost more than they save there)
+    ROUTER_PRODUCT_FROM = 128
     # False: every step on the per-pair kernels (for measurements and tests)
     use_grouped = True
 
@@ -80,7 +84,13 @@ class MoEMLP(FeedForward):
         router = self.router
         if router.dtype != xn.dtype:
             raise K.KernelError(f"the router's matrix is {router.dtype} in a {xn.dtype} run")
-        K.moe_route(xn, router, self.router_b, self.top, ids, weights)
+        if M >= self.ROUTER_PRODUCT_FROM and self.E <= 1024:
+            # many tokens: the logits as one matrix product (32-bit accumulation, the bias in its epilogue)
+            logits = torch.empty((M, self.E), dtype=torch.float32, device=xn.device)
+            linear(xn, router, logits, OUT_F32, self.router_b)
+            K.moe_select(logits, self.top, ids, weights)
+        else:
+            K.moe_route(xn, router, self.router_b, self.top, ids, weights)
         wd = self.wdown.view(self.E, self.d, self.F)
         if self.interleaved:
             wgu = self.wgu.view(self.E, self.F, 2, self.d)

@@ -199,6 +199,9 @@ def test_router_and_experts_alone(dtype, E, top, d, F):
     ids = torch.empty((M, top), dtype=torch.int32, device=DEV)
     wts = torch.empty((M, top), dtype=torch.float32, device=DEV)
     K.moe_route(x.to(tdt).to(DEV), wr.to(tdt).to(DEV), b.float().to(DEV), top, ids, wts)
+    # the selection alone, from logits made elsewhere (as steps of many tokens make them: one matrix product)
+    ids2, wts2 = torch.empty_like(ids), torch.empty_like(wts)
+    K.moe_select((x @ wr.T + b).float().to(DEV), top, ids2, wts2)
     res0 = rnd(M, d)
     res = res0.float().to(DEV)
     if dtype == "float32":
@@ -208,8 +211,9 @@ def test_router_and_experts_alone(dtype, E, top, d, F):
                       interleaved=True)
     for m in range(M):
         chosen, weights = P.route(wr @ x[m] + b, top)
-        assert ids[m].tolist() == chosen, m
+        assert ids[m].tolist() == chosen and ids2[m].tolist() == chosen, m
         assert max(abs(a - c) for a, c in zip(wts[m].tolist(), weights)) <= 2e-6
+        assert max(abs(a - c) for a, c in zip(wts2[m].tolist(), weights)) <= 2e-6
         y = sum(w_ * P.gated_ff(x[m:m + 1], wg[e], wu[e], wd[e])[0] for e, w_ in zip(chosen, weights))
         tol = 2e-5 if dtype == "float32" else 2e-2
         assert (res[m].double().cpu() - res0[m] - y).abs().max().item() <= tol * max(1.0, y.abs().max().item()), m
