@@ -39,7 +39,7 @@ def _ids(text: str) -> List[int]:
 
 
 def build_parser() -> argparse.ArgumentParser:
-    p = argparse.ArgumentParser(prog="rustyllm", description="Generate with a Llama model folder on one B200.",
+    p = argparse.ArgumentParser(prog="rustyllm", description="Generate with a model folder (Llama or Mosurax) on one B200.",
                                 formatter_class=argparse.RawDescriptionHelpFormatter, epilog=__doc__)
     p.add_argument("model_pos", nargs="?", metavar="model-dir", help="folder with config.json and model.safetensors")
     p.add_argument("--model", help="same as the positional model folder")
