@@ -30,16 +30,20 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
-                    help="most tokens live requests hold at any time, each rounded up to a multiple of 64")
+                    help="most tokens live requests hold at any time (the cache is sized for them, plus a page of "
+                         "slack for every request that can be live at once)")
     ap.add_argument("--device", default="cuda:0")
     args = ap.parse_args(argv)
 
     from ..kernels import PAGE_SIZE
     from .runner import Runner   # late: building the kernels prints progress lines
     os.makedirs(args.out, exist_ok=True)
-    pages = -(-args.max_tokens // PAGE_SIZE)     # the cache's own unit is the 64 tokens the option counts in
+    # The cache hands out pages of 64 positions, and every live request's last page is partly empty: N tokens
+    # spread over r requests can need ceil(N / 64) + r pages.  At most min(N, slots) requests are live at once.
+    slots = min(max(args.max_tokens, 1), 1024)
+    pages = -(-args.max_tokens // PAGE_SIZE) + min(slots, 256)
     runner, _ = Runner.from_path(args.model, dtype=args.dtype, device=args.device,
-                                 max_cache_tokens=pages * PAGE_SIZE, max_batch=min(max(pages, 1), 1024))
+                                 max_cache_tokens=pages * PAGE_SIZE, max_batch=slots)
     engine = runner.engine
     slot_of: Dict[str, int] = {}
     dev = torch.device(args.device)

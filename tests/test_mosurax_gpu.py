@@ -473,3 +473,31 @@ def test_greedy_generation_through_the_runner(dirs, name, dtype):
                     break
                 toks.append(t)
     r.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_trace_replay_of_short_requests_with_the_cache_sized_by_their_tokens(dirs, tmp_path, dtype):
+    """``bin/trace_run`` as a subprocess: nine requests of 3 to 40 tokens in one batch, decoded together, the
+    shorter ones ending earlier; ``--max-tokens`` is the number of tokens the live requests hold at most - not
+    rounded to pages, of which every request needs a last, partly empty one."""
+    from test_trace_gpu import read_step, run_trace
+    d = dirs["S"]
+    cfg, _ = _plain(d)
+    V = cfg["vocab"]
+    lens = [3, 40, 7, 12, 5, 33, 9, 21, 4]
+    extra = [0, 6, 2, 9, 1, 4, 9, 3, 5]
+    reqs = [random_tokens(V, n + e, 900 + i) for i, (n, e) in enumerate(zip(lens, extra))]
+    steps = [{"step": 0, "entries": [{"id": f"q{i}", "tokens": r[:n], "want": [0, n - 1]} for i, (r, n) in enumerate(zip(reqs, lens))],
+              "end": [f"q{i}" for i, e in enumerate(extra) if e == 0]}]
+    expect = {0: [(i, [0, n - 1]) for i, n in enumerate(lens)]}
+    for k in range(max(extra)):
+        live = [i for i, e in enumerate(extra) if e > k]
+        steps.append({"step": k + 1, "entries": [{"id": f"q{i}", "tokens": [reqs[i][lens[i] + k]], "want": [0]} for i in live],
+                      "end": [f"q{i}" for i in live if extra[i] == k + 1]})
+        expect[k + 1] = [(i, [lens[i] + k]) for i in live]
+    out_dir = str(tmp_path / dtype)
+    run_trace(d, dtype, steps, out_dir, max_tokens=sum(len(r) for r in reqs))
+    for step, exp in expect.items():
+        got = read_step(out_dir, step, V)
+        ref = torch.cat([plain_logits(d, reqs[i])[pos] for i, pos in exp])
+        close(got, ref, dtype, cfg, f"step {step}")
