@@ -133,8 +133,42 @@ def draw_weights(cfg, seed):
     return out
 
 
-def write_model(name, path, seed=None):
-    cfg = CONFIGS[name]
+def random_config(seed):
+    """A configuration with every size drawn at random: widths that are no multiple of 8 or 64, 1 to 8 heads
+    over any divisor of KV heads, key and value heads of 8 to 128 (equal or not), any window, 1 to 4 layers of
+    any feed-forward, any loop."""
+    import random
+    rng = random.Random(seed)
+    width = rng.choice([24, 40, 56, 72, 100, 136, 192, 204])
+    n = rng.randrange(1, 5)
+    layers = []
+    for _ in range(n):
+        heads = rng.choice([1, 2, 3, 4, 6, 8])
+        kv = rng.choice([g for g in range(1, heads + 1) if heads % g == 0])
+        dim = rng.choice([8, 16, 18, 24, 32, 48, 64, 64, 128, 128])
+        vdim = dim if rng.random() < 0.6 else rng.choice([8, 16, 20, 32, 64, 128])
+        window = rng.choice([None, 1, 2, 5, 33, 63, 64, 65, 100, 129, 1000])
+        kind = rng.choice(["dense", "moe", "moe", None])
+        if kind == "dense":
+            mlp = dense(rng.choice([8, 20, 64, 100, 136]))
+        elif kind == "moe":
+            E = rng.randrange(1, 10)
+            mlp = moe(E, rng.randrange(1, E + 1), rng.choice([8, 12, 16, 40, 64]), shared=rng.choice([None, 8, 24, 64]))
+        else:
+            mlp = None
+        layers.append(layer(attn(heads, kv, dim, vdim, rng.choice([0.05, 0.125, 0.3, 1.0 / math.sqrt(dim)]), window), mlp))
+    cfg = {"architecture": "Mosurax", "vocab": rng.choice([17, 64, 101, 300]), "width": width, "max_positions": 260,
+           "norm": {"eps": rng.choice([1e-6, 1e-5, 1e-3])}, "layers": layers}
+    if rng.random() < 0.7:
+        cfg["logit_softcap"] = rng.choice([2.0, 10.0, 50.0])
+    if rng.random() < 0.7:
+        a = rng.randrange(0, n)
+        cfg["loop"] = {"start": a, "stop": rng.randrange(a + 1, n + 1), "times": rng.randrange(1, 4)}
+    return cfg
+
+
+def write_model(name, path, seed=None, cfg=None):
+    cfg = cfg or CONFIGS[name]
     os.makedirs(path, exist_ok=True)
     with open(os.path.join(path, "config.json"), "w") as f:
         json.dump(cfg, f)
