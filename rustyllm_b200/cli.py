@@ -286,12 +286,31 @@ def run_kernel_benchmark(runner, runs: int, as_json: bool, layer_index: int = 0)
     rows.append(("attn_qkv.fused", timed(lambda: linear(xq, att.wqkv, qkv, OUT_SAME, att.bqkv)), att.wqkv.numel() * att.wqkv.element_size()))
     a = torch.randn(1, att.wo.shape[1], device=dev).to(att.wo.dtype)
     rows.append(("attn_output", timed(lambda: linear(a, att.wo, x, OUT_ADD_F32, att.bo)), att.wo.numel() * att.wo.element_size()))
-    gu = torch.empty(1, ff.wgu.shape[0], device=dev, dtype=ff.wgu.dtype)
-    xf = xn.to(ff.wgu.dtype)
-    rows.append(("ffn_gate_up.fused", timed(lambda: linear(xf, ff.wgu, gu, OUT_SAME, ff.bgu)), ff.wgu.numel() * ff.wgu.element_size()))
-    h = torch.empty(1, ff.I, device=dev, dtype=gu.dtype)
-    rows.append(("ffn_activation.silu_mul", timed(lambda: K.swiglu(gu, h)), 3 * ff.I * esz))
-    rows.append(("ffn_down", timed(lambda: linear(h, ff.wdown, x, OUT_ADD_F32, ff.bdown)), ff.wdown.numel() * ff.wdown.element_size()))
+    from .parts.mlp import GatedMLP
+    from .parts.moe import MoEMLP
+
+    def dense_rows(ff, tag):
+        gu = torch.empty(1, ff.wgu.shape[0], device=dev, dtype=ff.wgu.dtype)
+        xf = xn.to(ff.wgu.dtype)
+        rows.append((f"{tag}_gate_up.fused", timed(lambda: linear(xf, ff.wgu, gu, OUT_SAME, ff.bgu)), ff.wgu.numel() * ff.wgu.element_size()))
+        h = torch.empty(1, ff.I, device=dev, dtype=gu.dtype)
+        rows.append((f"{tag}_activation.silu_mul", timed(lambda: K.swiglu(gu, h, interleaved=ff.interleaved)), 3 * ff.I * esz))
+        rows.append((f"{tag}_down", timed(lambda: linear(h, ff.wdown, x, OUT_ADD_F32, ff.bdown)), ff.wdown.numel() * ff.wdown.element_size()))
+
+    if isinstance(ff, GatedMLP):
+        dense_rows(ff, "ffn")
+    elif isinstance(ff, MoEMLP):          # router and the chosen experts of one token; the shared expert like a dense one
+        xe = xn.to(ff.router.dtype)
+        ids = torch.empty((1, ff.top), dtype=torch.int32, device=dev)
+        wts = torch.empty((1, ff.top), dtype=torch.float32, device=dev)
+        rows.append(("ffn_router", timed(lambda: K.moe_route(xe, ff.router, ff.router_b, ff.top, ids, wts)), ff.router.numel() * esz))
+        shared, ff.shared = ff.shared, None
+        try:
+            rows.append(("ffn_experts.chosen", timed(lambda: ff.forward(xe, x, None)), ff.router.numel() * esz + ff.top * 3 * ff.F * ff.d * esz))
+        finally:
+            ff.shared = shared
+        if shared is not None and isinstance(shared, GatedMLP):
+            dense_rows(shared, "ffn_shared")
     head = runner.model.head
     logits = torch.empty(1, head.V, device=dev)
     xh = xn.to(head.weight.dtype)
@@ -304,13 +323,19 @@ def run_kernel_benchmark(runner, runs: int, as_json: bool, layer_index: int = 0)
             break
         s = eng.alloc_slot()
         eng.step([s], [[1] * ctx], None)
-        group, layer = runner.cache.kv_entry(layer_index)
+        m = runner.model      # the cache entry of the layer's first run (a looped layer has one a run)
+        entry = next(e for pos, (e, _) in enumerate(m.run_entry) if m.spec.schedule[pos] == layer_index)
+        group, layer = runner.cache.kv_entry(entry)
         st = eng.step_state(torch.tensor([1, ctx, s, 0, 1, s, ctx + 1, 0], dtype=torch.int32, device=dev), (1, 1, 1), [1], [ctx + 1])
         runner.cache.prepare([s], [1])
         q = torch.randn(1, qkv.shape[1], device=dev).to(dt)
-        o = torch.empty(1, att.H * att.hd, device=dev, dtype=dt)
-        t = timed(lambda: K.attention(q, group.k_pool(layer), group.v_pool(layer), group.page_table, st, o, att.H, att.G, att.hd, att.scale))
-        rows.append((f"attn_scan.ctx{ctx}", t, 2 * (ctx + 1) * att.G * att.hd * esz))
+        o = torch.empty(1, att.H * att.vd, device=dev, dtype=dt)
+        n_qkv = (att.H + att.G) * att.hd + att.G * att.vd
+        gate = q[:, n_qkv:] if getattr(att, "gated", False) else None
+        t = timed(lambda: K.attention(q, group.k_pool(layer), group.v_pool(layer), group.page_table, st, o, att.H, att.G, att.hd, att.scale,
+                                      att.window or 0, value_dim=att.vd, sink=getattr(att, "sink", False), gate=gate))
+        seen = min(ctx + 1, att.window) if att.window else ctx + 1
+        rows.append((f"attn_scan.ctx{ctx}", t, seen * att.G * (att.hd + att.vd) * esz))
         eng.free_slot(s)
     if as_json:
         # the reference's envelope (src/main.rs:1672-1676): "type" names the record, "format" its layout

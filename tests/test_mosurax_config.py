@@ -109,3 +109,11 @@ def test_plain_mechanisms_on_values_worked_out_by_hand():
     x = torch.tensor([[3.0, 4.0]], dtype=torch.float64)
     assert torch.allclose(P.rms_norm(x, torch.ones(2, dtype=torch.float64), 0.0), x / math.sqrt(12.5))
     assert abs(float(P.soft_cap(torch.tensor([1e9], dtype=torch.float64), 5.0)) - 5.0) < 1e-9
+
+
+def test_command_line_inspects_a_folder(tmp_path, capsys):
+    from rustyllm_b200 import cli
+    d = C.write_model("S", str(tmp_path / "S"))
+    assert cli.main([d, "--inspect", "--list-tensors"]) == 0
+    out = capsys.readouterr().out
+    assert "architecture: Mosurax" in out and "compatibility: supported" in out and "l1.mlp.e6.down" in out and "width: 48" in out

@@ -501,3 +501,24 @@ def test_trace_replay_of_short_requests_with_the_cache_sized_by_their_tokens(dir
         got = read_step(out_dir, step, V)
         ref = torch.cat([plain_logits(d, reqs[i])[pos] for i, pos in exp])
         close(got, ref, dtype, cfg, f"step {step}")
+
+
+def test_command_line_generates_benchmarks_and_times_kernels(dirs, capsys, tmp_path):
+    """``bin/rustyllm``'s entry point on a Mosurax folder: greedy ids equal the plain loop's, the benchmark and the
+    kernel benchmark run (the latter on a layer of experts and on a dense one, from random weights)."""
+    import json
+    from rustyllm_b200 import cli
+    d = dirs["P"]
+    cfg, w = _plain(d)
+    prompt = random_tokens(cfg["vocab"], 9, 81)
+    assert cli.main([d, "--dtype", "float32", "-p", " ".join(map(str, prompt)), "-n", "5", "-t", "0", "--ignore-eos"]) == 0
+    assert [int(t) for t in capsys.readouterr().out.split()] == P.greedy(cfg, w, prompt, 5)
+    assert cli.main([d, "--bench-json", "--bench-runs", "2", "--batch", "3", "--prompt-len", "20", "-n", "4", "--seed", "5", "--ignore-eos"]) == 0
+    rep = json.loads(capsys.readouterr().out)
+    assert rep["architecture"] == "Mosurax" and rep["results"][0]["prompt_tokens"] == 60 and rep["results"][0]["generated_tokens"] == 12
+    for layer, names in ((0, ("attn_qkv.fused", "ffn_gate_up.fused", "ffn_down", "attn_scan.ctx128")),
+                         (1, ("ffn_router", "ffn_experts.chosen", "ffn_shared_gate_up.fused", "output"))):
+        assert cli.main([d, "--random", "--kernel-bench-json", "--kernel-bench-runs", "3", "--kernel-bench-layer", str(layer)]) == 0
+        rows = {r["name"]: r for r in json.loads(capsys.readouterr().out)["rows"]}
+        for name in names:
+            assert rows[name]["avg_us"] > 0, name
