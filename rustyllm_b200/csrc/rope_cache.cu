@@ -129,6 +129,25 @@ rope_kv_write_bf16_half_kernel(__nv_bfloat16* __restrict__ qkv, int ld, const in
   }
 }
 
+// No rotation at all (rotary width 0): keys and values go to their pages as they are, 16 bytes a thread;
+// the queries stay where they are.  One CTA a token; any dtype (bytes are copied).
+__global__ void __launch_bounds__(ROPE_THREADS)
+kv_write_copy_kernel(const uint4* __restrict__ qkv, int ld16, const int* __restrict__ positions,
+                     const int* __restrict__ slot_of_token, const int* __restrict__ page_table, int max_pages,
+                     int q16, int G, int hd16, int vd16, uint4* __restrict__ k_pool, uint4* __restrict__ v_pool) {
+  rl_pdl_trigger();
+  rl_pdl_wait();
+  const int m = blockIdx.x;
+  const int pos = positions[m];
+  const int page = page_table[(size_t)slot_of_token[m] * max_pages + pos / RL_PAGE];
+  const uint4* row = qkv + (size_t)m * ld16 + q16;             // behind the query heads: G key heads, then G value heads
+  uint4* kd = k_pool + ((size_t)page * G * RL_PAGE + pos % RL_PAGE) * hd16;
+  uint4* vd = v_pool + ((size_t)page * G * RL_PAGE + pos % RL_PAGE) * vd16;
+  for (int i = threadIdx.x; i < G * hd16; i += ROPE_THREADS) kd[(size_t)(i / hd16) * RL_PAGE * hd16 + i % hd16] = row[i];
+  row += G * hd16;
+  for (int i = threadIdx.x; i < G * vd16; i += ROPE_THREADS) vd[(size_t)(i / vd16) * RL_PAGE * vd16 + i % vd16] = row[i];
+}
+
 // qkv: [M, ld] holding per token H query heads and G key heads of head_dim, then G value
 // heads of value_dim (even; it may differ from head_dim).  Queries are rotated in place;
 // rotated keys go to k_pool [pages, G, RL_PAGE, head_dim] and the values to v_pool
@@ -151,7 +170,14 @@ extern "C" int rl_rope_kv_write(void* qkv, int dtype, int ld, const int* positio
   RL_REQUIRE(head_dim % 2 == 0, "rl_rope_kv_write: head_dim %d must be even", head_dim);
   const dim3 grid(num_tokens, (num_heads + 2 * num_kv_heads + ROPE_HEADS_PER_CTA - 1) / ROPE_HEADS_PER_CTA);
   const int threads = ROPE_THREADS;
-  if (dtype == RL_BF16 && write_cache && !interleaved && rotary_dim == head_dim && value_dim == head_dim && head_dim % 16 == 0 && ld % 8 == 0 &&
+  const int esz = dtype == RL_F32 ? 4 : 2;
+  if (rotary_dim == 0 && !write_cache) return RL_OK;          // nothing to rotate, nothing to store
+  if (rotary_dim == 0 && (dtype == RL_F32 || dtype == RL_BF16) && (head_dim * esz) % 16 == 0 && (value_dim * esz) % 16 == 0 &&
+      (ld * esz) % 16 == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)k_pool & 15) == 0 && ((uintptr_t)v_pool & 15) == 0)
+    rl_launch_pdl(kv_write_copy_kernel, dim3(num_tokens), threads, 0, stream, (const uint4*)qkv, ld * esz / 16, positions,
+                  slot_of_token, page_table, max_pages, num_heads * head_dim * esz / 16, num_kv_heads, head_dim * esz / 16,
+                  value_dim * esz / 16, (uint4*)k_pool, (uint4*)v_pool);
+  else if (dtype == RL_BF16 && write_cache && !interleaved && rotary_dim == head_dim && value_dim == head_dim && head_dim % 16 == 0 && ld % 8 == 0 &&
       ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)k_pool & 15) == 0 && ((uintptr_t)v_pool & 15) == 0)
     rl_launch_pdl(rope_kv_write_bf16_half_kernel,
                   dim3(num_tokens, (num_heads + 2 * num_kv_heads + ROPE_FAST_HEADS_PER_CTA - 1) / ROPE_FAST_HEADS_PER_CTA),
