@@ -630,7 +630,7 @@ extern "C" int rl_attention_prefill_tc_supported(int num_heads, int num_kv_heads
   return head_dim == 64 || head_dim == 128;
 }
 
-// Same contract as rl_attention_prefill, with num_tiles = sum over sequences of
+// Same interface as rl_attention_prefill, with num_tiles = sum over sequences of
 // ceil(tokens / 128), num_pages = pages in the cache pools, and err = device int that is set
 // non-zero if a bounded wait in the kernel ran out.  tile_order (may be null): num_tiles pairs
 // (sequence, tile of the sequence), every tile of the step once, in the order the blocks should

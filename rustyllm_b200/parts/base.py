@@ -24,7 +24,7 @@ Roles and what each must provide:
     ``cache`` is this layer run's ``CacheView`` (key/value pools and page table,
     state area, and whether this layer writes them or only reads another's).
 ``FeedForward``
-    ``forward(xn, residual, step) -> None``: same contract without a cache.
+    ``forward(xn, residual, step) -> None``: the same without a cache.
 ``Block``
     Built from (mixer, mixer_norm, feed_forward, feed_forward_norm);
     ``forward(x, step, cache, pending=None, next_norm=None)`` updates the residual x in
