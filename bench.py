@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the Llama-3.1-8B shape with random bf16 weights on
 one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--layers L] [--impl reference] [--designs]
 
 Prints ONE JSON line.  ``value``: decoded tokens a second at a batch of 8 (K single-token
 steps timed on the device with CUDA events after W warm-up steps).  ``e2e``: the same
@@ -16,6 +16,12 @@ copy bandwidth.  ``points``: decode at batch 1 and 64.
 
 Weights (15 GB) are far larger than the L2 cache, so every timed step reads them from
 HBM; no extra flush is needed.
+
+    python bench.py --designs
+
+is another program under the same name: prompt and single-token throughput of the Mosurax design beside
+the Llama decoder at two layer sizes of real models (``rustyllm_b200/bench_designs.py``), one JSON line a
+model and one with the ratios a size.  The headline workload above and its one line are untouched by it.
 """
 import argparse
 import json
