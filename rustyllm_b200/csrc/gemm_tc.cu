@@ -412,9 +412,12 @@ struct TcTail {
   int t0_first;      // first token that is not covered by full-width tiles there
   int count_first;   // narrow tiles in that weight-row tile
   int per_n;         // narrow tiles in every weight-row tile after it
+  int tiles_n;       // > 0: the walk goes token tile by token tile (all weight-row tiles of one before the next), for
+                     // grouped products: the CTAs that run together then share few groups' weights and token tiles
 };
 struct TcTileAt { int n0, m0, bt; };
 __device__ __forceinline__ TcTileAt tc_tile_at(int tile, int tiles_m, int BT, const TcTail& t) {
+  if (t.tiles_n > 0) return {(tile % t.tiles_n) * BLOCK_N_OUT, (tile / t.tiles_n) * BT, BT};
   if (tile < t.first) return {(tile / tiles_m) * BLOCK_N_OUT, (tile % tiles_m) * BT, BT};
   int idx = tile - t.first;
   if (idx < t.count_first) return {t.n_first * BLOCK_N_OUT, t.t0_first + idx * t.bt, t.bt};
@@ -590,7 +593,7 @@ static int launch_tc_persistent(const CUtensorMap& mw, const CUtensorMap& ma, co
   // the tiles behind the last full wave: the narrowest token tile (from 64 tokens: below, the
   // weight tile's trip through shared memory takes longer than the products) that leaves no
   // more of them than there are CTAs
-  TcTail tail = {total, BT, 0, 0, 0, 1};
+  TcTail tail = {total, BT, 0, 0, 0, 1, tile_group != nullptr ? tiles_n : 0};
   int num_tiles = total;
   const int full = (total / num_sms) * num_sms;
   if (full < total && tile_group == nullptr) {      // grouped: a narrow tile could lie across two groups' rows
