@@ -14,6 +14,7 @@ from .engine.generate import GenerationOptions, GenerationResult, GenerationStat
 from .engine.runner import LoadInfo, Runner  # noqa: F401
 from .engine.step import Engine  # noqa: F401
 from .models import llama as _llama  # noqa: F401  (registers the architecture)
+from .models import mogutar as _mogutar  # noqa: F401
 from .models import mosurax as _mosurax  # noqa: F401
 from .sampling.config import Rng, SamplerConfig  # noqa: F401
 from .weights.loader import WeightsError  # noqa: F401

@@ -11,7 +11,8 @@ sequence.  Here one pool serves every sequence of every batch:
   * a *slot* holds one sequence: its length, one row of each group's page table,
     and ``state_bytes`` of state that is zeroed when the slot is handed out;
   * a *group* is the storage of all layers with the same need (number of KV
-    heads, width of a key head and of a value head, all keys or a window of them).
+    heads, width of a key head and of a value head, all keys or a window of them, with
+    or without first positions that stay).
     It owns the keys ``[layers, pages, kv_heads, page_size, head_dim]``, the values
     ``[layers, pages, kv_heads, page_size, value_dim]`` and a page allocator;
     page p of a slot holds positions ``[p*page_size, (p+1)*page_size)`` of every
@@ -41,8 +42,11 @@ class KVNeed:
     head_dim: int                  # width of a key head
     window: Optional[int] = None   # None: all keys; W: only the last W positions are read
     value_dim: Optional[int] = None  # width of a value head; None: the same as head_dim
+    keep_first: int = 0            # with a window: positions [0, keep_first) stay readable for good
 
     def __post_init__(self):
+        if self.window is None and self.keep_first:
+            object.__setattr__(self, "keep_first", 0)   # without a window everything stays anyway
         if self.value_dim == self.head_dim:        # one way to say "the same": equal needs share a group
             object.__setattr__(self, "value_dim", None)
 
@@ -243,11 +247,12 @@ class SequenceCache:
                 # the next query sits at position len; it reads positions >= len + 1 - w
                 first_needed = max(0, self.lengths[s] + 1 - w)
                 dead = first_needed // PAGE_SIZE   # logical pages wholly in front of it
+                kept = -(-g.need.keep_first // PAGE_SIZE)   # pages that hold a position the window never drops
                 sp = g.slot_pages[s]
-                gone = [sp[i] for i in range(min(dead, len(sp))) if sp[i] >= 0]
+                gone = [sp[i] for i in range(kept, min(dead, len(sp))) if sp[i] >= 0]
                 if gone:
                     g.pages.give_back(gone)
-                    for i in range(min(dead, len(sp))):
+                    for i in range(kept, min(dead, len(sp))):
                         sp[i] = -1
 
     # ------------------------------------------------------------------ views for parts

@@ -30,7 +30,7 @@ attention_simt_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k_
                       const T* __restrict__ v_pool, const int* __restrict__ page_table, int max_pages,
                       const int* __restrict__ slot_of_token, const int* __restrict__ positions,
                       T* __restrict__ out, int ldo, int H, int G, int hd, int vd, float scale, int window,
-                      int sink, const T* __restrict__ gate, int ldg) {
+                      int sink, const T* __restrict__ gate, int ldg, float softcap, int keep_first) {
   constexpr int NE = ATT_MAX_HD / 32;
   __shared__ float s_acc[ATT_WARPS][ATT_MAX_HD];
   __shared__ float s_max[ATT_WARPS], s_sum[ATT_WARPS];
@@ -49,6 +49,11 @@ attention_simt_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k_
   }
 
   const int start = (window > 0 && pos + 1 - window > 0) ? pos + 1 - window : 0;
+  // kept first tokens: positions [0, nfirst) in front of the window are seen as well.  The keys are walked
+  // as one run of `total` places: place v is position v for v < nfirst and start + (v - nfirst) behind.
+  const int nfirst = min(keep_first, start);
+  const int total = nfirst + pos - start + 1;
+  const float inv_cap = softcap > 0.f ? 1.0f / softcap : 0.f;
   float acc[NE];
 #pragma unroll
   for (int e = 0; e < NE; ++e) acc[e] = 0.f;
@@ -56,11 +61,11 @@ attention_simt_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k_
   const size_t head_off = (size_t)g * RL_PAGE * hd, v_head_off = (size_t)g * RL_PAGE * vd;
   const size_t page_stride = (size_t)G * RL_PAGE * hd, v_page_stride = (size_t)G * RL_PAGE * vd;
 
-  for (int t0 = start + 32 * warp; t0 <= pos; t0 += 32 * ATT_WARPS) {
-    const int n = min(32, pos - t0 + 1);
-    float s = -INFINITY;              // lane j: the score of key t0 + j
+  for (int v0 = 32 * warp; v0 < total; v0 += 32 * ATT_WARPS) {
+    const int n = min(32, total - v0);
+    float s = -INFINITY;              // lane j: the score of the key at place v0 + j
     for (int j = 0; j < n; ++j) {
-      const int tj = t0 + j;
+      const int tj = v0 + j < nfirst ? v0 + j : start + (v0 + j - nfirst);
       const T* krow = k_pool + (size_t)pages[tj / RL_PAGE] * page_stride + head_off + (size_t)(tj % RL_PAGE) * hd;
       float part = 0.f;
 #pragma unroll
@@ -71,7 +76,9 @@ attention_simt_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k_
       const float sj = rl_warp_sum(part);
       if (lane == j) s = sj;
     }
-    const float new_max = fmaxf(run_max, rl_warp_max(s));   // finite: key t0 is valid
+    if (softcap > 0.f) s = softcap * tanhf(s * inv_cap);      // tanh(-inf) = -1 on lanes without a key: masked below
+    if (lane >= n) s = -INFINITY;
+    const float new_max = fmaxf(run_max, rl_warp_max(s));   // finite: the chunk's first key is valid
     const float corr = expf(run_max - new_max);              // exp(-inf) = 0 on the warp's first chunk
     const float p = (lane < n) ? expf(s - new_max) : 0.f;
     run_sum = run_sum * corr + rl_warp_sum(p);
@@ -80,7 +87,7 @@ attention_simt_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k_
     for (int e = 0; e < NE; ++e) acc[e] *= corr;
     for (int j = 0; j < n; ++j) {
       const float pj = __shfl_sync(0xffffffffu, p, j);
-      const int tj = t0 + j;
+      const int tj = v0 + j < nfirst ? v0 + j : start + (v0 + j - nfirst);
       const T* vrow = v_pool + (size_t)pages[tj / RL_PAGE] * v_page_stride + v_head_off + (size_t)(tj % RL_PAGE) * vd;
 #pragma unroll
       for (int e = 0; e < NE; ++e) {
@@ -127,11 +134,16 @@ attention_simt_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k_
 // sink != 0: the softmax has one more term in its denominator, of score 0 and without a value.
 // gate (may be null): [M, ldg], same dtype; head h's output is multiplied element by element with
 // sigmoid(gate[m, h*vd + i]) before it is stored.
-extern "C" int rl_attention_simt_gated(const void* q, int ldq, const void* k_pool, const void* v_pool,
-                                       int dtype, const int* page_table, int max_pages,
-                                       const int* slot_of_token, const int* positions, void* out, int ldo,
-                                       int num_tokens, int num_heads, int num_kv_heads, int head_dim, int value_dim,
-                                       float scale, int window, int sink, const void* gate, int ldg, cudaStream_t stream) {
+//
+// softcap > 0: every score s (scale included) becomes softcap * tanh(s / softcap).  keep_first > 0 (with a window):
+// a query also sees positions [0, keep_first) that the window has left behind.
+extern "C" int rl_attention_simt_masked(const void* q, int ldq, const void* k_pool, const void* v_pool,
+                                        int dtype, const int* page_table, int max_pages,
+                                        const int* slot_of_token, const int* positions, void* out, int ldo,
+                                        int num_tokens, int num_heads, int num_kv_heads, int head_dim, int value_dim,
+                                        float scale, int window, int sink, const void* gate, int ldg, float softcap,
+                                        int keep_first, cudaStream_t stream) {
+  RL_REQUIRE(softcap >= 0.f && keep_first >= 0, "rl_attention_simt: negative soft cap or number of kept first tokens");
   RL_REQUIRE(gate == nullptr || ldg >= num_heads * value_dim, "rl_attention_simt: the gate's row stride is too small");
   RL_REQUIRE(num_tokens >= 0 && num_heads > 0 && num_kv_heads > 0, "rl_attention_simt: bad sizes");
   RL_REQUIRE(num_heads % num_kv_heads == 0, "rl_attention_simt: %d heads are no multiple of %d KV heads",
@@ -147,16 +159,26 @@ extern "C" int rl_attention_simt_gated(const void* q, int ldq, const void* k_poo
     attention_simt_kernel<float><<<grid, ATT_WARPS * 32, 0, stream>>>(
         (const float*)q, ldq, (const float*)k_pool, (const float*)v_pool, page_table, max_pages,
         slot_of_token, positions, (float*)out, ldo, num_heads, num_kv_heads, head_dim, value_dim, scale, window,
-        sink, (const float*)gate, ldg);
+        sink, (const float*)gate, ldg, softcap, keep_first);
   else if (dtype == RL_BF16)
     attention_simt_kernel<__nv_bfloat16><<<grid, ATT_WARPS * 32, 0, stream>>>(
         (const __nv_bfloat16*)q, ldq, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, page_table,
         max_pages, slot_of_token, positions, (__nv_bfloat16*)out, ldo, num_heads, num_kv_heads, head_dim, value_dim, scale, window,
-        sink, (const __nv_bfloat16*)gate, ldg);
+        sink, (const __nv_bfloat16*)gate, ldg, softcap, keep_first);
   else
     RL_REQUIRE(false, "rl_attention_simt: unknown dtype %d", dtype);
   RL_LAUNCH_CHECK("rl_attention_simt");
   return RL_OK;
+}
+
+extern "C" int rl_attention_simt_gated(const void* q, int ldq, const void* k_pool, const void* v_pool,
+                                       int dtype, const int* page_table, int max_pages,
+                                       const int* slot_of_token, const int* positions, void* out, int ldo,
+                                       int num_tokens, int num_heads, int num_kv_heads, int head_dim, int value_dim,
+                                       float scale, int window, int sink, const void* gate, int ldg, cudaStream_t stream) {
+  return rl_attention_simt_masked(q, ldq, k_pool, v_pool, dtype, page_table, max_pages, slot_of_token, positions, out, ldo,
+                                  num_tokens, num_heads, num_kv_heads, head_dim, value_dim, scale, window, sink, gate, ldg, 0.f, 0,
+                                  stream);
 }
 
 extern "C" int rl_attention_simt(const void* q, int ldq, const void* k_pool, const void* v_pool,

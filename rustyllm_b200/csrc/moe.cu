@@ -38,15 +38,10 @@ __device__ __forceinline__ float moe_dot8(const float* w, const float* xs) {
 }
 
 // ------------------------------------------------------------------ router
-// One block a token; warp w takes experts w, w + 8, ...; then warp 0 selects.
+// The logits of block m's token into s_logit[E] (s_x [d] is scratch): warp w takes experts w, w + 8, ...
 template <typename T>
-__global__ void __launch_bounds__(MOE_THREADS)
-moe_route_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ wr, const float* __restrict__ bias,
-                 int d, int E, int top, int* __restrict__ ids, float* __restrict__ weights) {
-  extern __shared__ float s_logit[];     // [E], then the token's input [d]
-  float* s_x = s_logit + ((E + 3) & ~3);
-  rl_pdl_trigger();
-  rl_pdl_wait();
+__device__ __forceinline__ void moe_logits(const T* __restrict__ x, int ldx, const T* __restrict__ wr, const float* __restrict__ bias,
+                                           int d, int E, float* s_logit, float* s_x) {
   const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const T* xr = x + (size_t)m * ldx;
   for (int i = threadIdx.x; i < d; i += MOE_THREADS) s_x[i] = rl_ld(xr + i);
@@ -64,6 +59,19 @@ moe_route_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ wr, con
     if (lane == 0) s_logit[e] = part + (bias ? bias[e] : 0.f);
   }
   __syncthreads();
+}
+
+// One block a token; then warp 0 selects.
+template <typename T>
+__global__ void __launch_bounds__(MOE_THREADS)
+moe_route_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ wr, const float* __restrict__ bias,
+                 int d, int E, int top, int* __restrict__ ids, float* __restrict__ weights) {
+  extern __shared__ float s_logit[];     // [E], then the token's input [d]
+  float* s_x = s_logit + ((E + 3) & ~3);
+  rl_pdl_trigger();
+  rl_pdl_wait();
+  const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  moe_logits(x, ldx, wr, bias, d, E, s_logit, s_x);
   if (warp != 0) return;
   float chosen = 0.f, first = 0.f, denom = 0.f;      // lane c keeps choice c's logit
   int chosen_id = 0;
@@ -163,6 +171,151 @@ extern "C" int rl_moe_route(const void* x, int ldx, const void* router, const fl
   else
     RL_REQUIRE(false, "rl_moe_route: unknown dtype %d", dtype);
   RL_LAUNCH_CHECK("rl_moe_route");
+  return RL_OK;
+}
+
+// ------------------------------------------------------------------ router with sigmoid scores
+// scores s = sigmoid(z); an expert is chosen by s + correction[e] ("choice score"), weighed by s itself (not
+// renormalised).  Experts form `groups` equal groups of neighbours; a group's score is the sum of its two
+// largest choice scores (of its one, in groups of one); only experts of the `keep` best groups can be chosen.
+// Ties go to the lower index.  One warp: s_score [E] holds the logits on entry, s_choice [E] and s_group
+// [2 * groups] are scratch.
+__device__ __forceinline__ void moe_pick_sigmoid(float* s_score, float* s_choice, float* s_group, const float* __restrict__ correction,
+                                                 int E, int top, int groups, int keep, int lane, int* __restrict__ ids,
+                                                 float* __restrict__ weights) {
+  for (int e = lane; e < E; e += 32) {
+    const float sc = 1.0f / (1.0f + expf(-s_score[e]));
+    s_score[e] = sc;
+    s_choice[e] = sc + (correction ? correction[e] : 0.f);
+  }
+  __syncwarp();
+  if (groups > 1 && keep < groups) {
+    const int size = E / groups;
+    for (int g = lane; g < groups; g += 32) {
+      float t1 = -INFINITY, t2 = -INFINITY;
+      for (int e = g * size; e < (g + 1) * size; ++e) {
+        const float v = s_choice[e];
+        if (v > t1) { t2 = t1; t1 = v; }
+        else if (v > t2) t2 = v;
+      }
+      s_group[g] = size > 1 ? t1 + t2 : t1;
+      s_group[groups + g] = 0.f;           // 1: the group is kept
+    }
+    __syncwarp();
+    for (int c = 0; c < keep; ++c) {
+      float best = -INFINITY;
+      int at = 0x7fffffff;
+      for (int g = lane; g < groups; g += 32) {
+        const float v = s_group[g];
+        if (s_group[groups + g] == 0.f && (v > best || at == 0x7fffffff)) { best = v; at = g; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+        if (oa != 0x7fffffff && (at == 0x7fffffff || ob > best || (ob == best && oa < at))) { best = ob; at = oa; }
+      }
+      __syncwarp();
+      if (lane == 0 && at != 0x7fffffff) s_group[groups + at] = 1.f;
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32)
+      if (s_group[groups + e / size] == 0.f) s_choice[e] = -INFINITY;
+    __syncwarp();
+  }
+  float chosen_w = 0.f;
+  int chosen_id = 0;
+  for (int c = 0; c < top; ++c) {
+    float best = -INFINITY;
+    int at = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) {
+      const float z = s_choice[e];
+      if (z > best) { best = z; at = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+      if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+    }
+    if (at == 0x7fffffff) at = 0;
+    if (lane == c) { chosen_id = at; chosen_w = s_score[at]; }
+    __syncwarp();
+    if (lane == 0) s_choice[at] = -INFINITY;
+    __syncwarp();
+  }
+  if (lane < top) {
+    ids[lane] = chosen_id;
+    weights[lane] = chosen_w;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(MOE_THREADS)
+moe_route_sigmoid_kernel(const T* __restrict__ x, int ldx, const T* __restrict__ wr, const float* __restrict__ correction,
+                         int d, int E, int top, int groups, int keep, int* __restrict__ ids, float* __restrict__ weights) {
+  extern __shared__ float s_logit[];     // scores [E], choice scores [E], groups [2 * groups], then the token's input [d]
+  const int Ep = (E + 3) & ~3;
+  float* s_x = s_logit + 4 * Ep;
+  rl_pdl_trigger();
+  rl_pdl_wait();
+  moe_logits(x, ldx, wr, (const float*)nullptr, d, E, s_logit, s_x);
+  if (threadIdx.x >= 32) return;
+  const size_t m = blockIdx.x;
+  moe_pick_sigmoid(s_logit, s_logit + Ep, s_logit + 2 * Ep, correction, E, top, groups, keep, threadIdx.x, ids + m * top, weights + m * top);
+}
+
+// from logits a matrix product has made: one warp a token
+__global__ void __launch_bounds__(32)
+moe_select_sigmoid_kernel(const float* __restrict__ logits, int E, int top, const float* __restrict__ correction, int groups, int keep,
+                          int* __restrict__ ids, float* __restrict__ weights) {
+  extern __shared__ float s_logit[];
+  const int Ep = (E + 3) & ~3;
+  rl_pdl_trigger();
+  rl_pdl_wait();
+  const size_t m = blockIdx.x;
+  for (int e = threadIdx.x; e < E; e += 32) s_logit[e] = logits[m * E + e];
+  __syncwarp();
+  moe_pick_sigmoid(s_logit, s_logit + Ep, s_logit + 2 * Ep, correction, E, top, groups, keep, threadIdx.x, ids + m * top, weights + m * top);
+}
+
+static int moe_sigmoid_args(const char* who, int num_experts, int top, int groups, int keep) {
+  RL_REQUIRE(num_experts > 0 && num_experts <= 1024, "%s: %d experts (at most 1,024)", who, num_experts);
+  RL_REQUIRE(top > 0 && top <= num_experts && top <= MOE_MAX_TOP, "%s: top %d must lie in [1, min(%d, %d)]", who, top, num_experts, MOE_MAX_TOP);
+  RL_REQUIRE(groups >= 1 && num_experts % groups == 0 && keep >= 1 && keep <= groups, "%s: %d groups (keep %d) do not divide %d experts", who,
+             groups, keep, num_experts);
+  RL_REQUIRE(keep * (num_experts / groups) >= top, "%s: the %d kept groups hold fewer than top = %d experts", who, keep, top);
+  return RL_OK;
+}
+
+extern "C" int rl_moe_select_sigmoid(const float* logits, int num_tokens, int num_experts, int top, const float* correction, int groups,
+                                     int keep, int* ids, float* weights, cudaStream_t stream) {
+  RL_REQUIRE(num_tokens >= 0, "rl_moe_select_sigmoid: bad sizes");
+  if (const int rc = moe_sigmoid_args("rl_moe_select_sigmoid", num_experts, top, groups, keep)) return rc;
+  if (num_tokens == 0) return RL_OK;
+  const size_t smem = (size_t)4 * ((num_experts + 3) & ~3) * sizeof(float);
+  rl_launch_pdl(moe_select_sigmoid_kernel, num_tokens, 32, smem, stream, logits, num_experts, top, correction, groups, keep, ids, weights);
+  RL_LAUNCH_CHECK("rl_moe_select_sigmoid");
+  return RL_OK;
+}
+
+extern "C" int rl_moe_route_sigmoid(const void* x, int ldx, const void* router, const float* correction, int dtype, int num_tokens,
+                                    int hidden, int num_experts, int top, int groups, int keep, int* ids, float* weights,
+                                    cudaStream_t stream) {
+  RL_REQUIRE(num_tokens >= 0 && hidden > 0, "rl_moe_route_sigmoid: bad sizes M=%d d=%d", num_tokens, hidden);
+  if (const int rc = moe_sigmoid_args("rl_moe_route_sigmoid", num_experts, top, groups, keep)) return rc;
+  if (num_tokens == 0) return RL_OK;
+  RL_REQUIRE(hidden + 4 * num_experts <= 11000, "rl_moe_route_sigmoid: hidden size plus four times the experts above 11,000");
+  const size_t smem = (size_t)(4 * ((num_experts + 3) & ~3) + hidden) * sizeof(float);
+  if (dtype == RL_F32)
+    rl_launch_pdl(moe_route_sigmoid_kernel<float>, num_tokens, MOE_THREADS, smem, stream, (const float*)x, ldx, (const float*)router,
+                  correction, hidden, num_experts, top, groups, keep, ids, weights);
+  else if (dtype == RL_BF16)
+    rl_launch_pdl(moe_route_sigmoid_kernel<__nv_bfloat16>, num_tokens, MOE_THREADS, smem, stream, (const __nv_bfloat16*)x, ldx,
+                  (const __nv_bfloat16*)router, correction, hidden, num_experts, top, groups, keep, ids, weights);
+  else
+    RL_REQUIRE(false, "rl_moe_route_sigmoid: unknown dtype %d", dtype);
+  RL_LAUNCH_CHECK("rl_moe_route_sigmoid");
   return RL_OK;
 }
 

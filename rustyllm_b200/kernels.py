@@ -47,6 +47,25 @@ _SIGNATURES = {
     "rl_attention_simt_gated": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
                                 _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
                                 _c_int, _c_void_p, _c_int, _c_void_p],
+    "rl_attention_simt_masked": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p,
+                                 _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
+                                 _c_int, _c_void_p, _c_int, _c_float, _c_int, _c_void_p],
+    "rl_short_conv": [_c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_ll,
+                      _c_void_p, _c_int, _c_int, _c_void_p],
+    "rl_short_conv_state": [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_ll, _c_void_p],
+    "rl_qkv_prepare": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_ll, _c_void_p, _c_void_p,
+                       _c_float, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_float, _c_int, _c_int, _c_int,
+                       _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
+    "rl_linear_scan": [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p,
+                       _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_ll, _c_void_p, _c_int, _c_int,
+                       _c_int, _c_int, _c_int, _c_void_p],
+    "rl_norm_add": [_c_void_p, _c_void_p, _c_float, _c_void_p, _c_float, _c_void_p, _c_float, _c_int, _c_int, _c_void_p, _c_void_p],
+    "rl_gated_norm": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_float, _c_int, _c_int, _c_int,
+                      _c_void_p, _c_int, _c_void_p],
+    "rl_gelu_gate": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p],
+    "rl_moe_route_sigmoid": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                             _c_void_p, _c_void_p, _c_void_p],
+    "rl_moe_select_sigmoid": [_c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
     "rl_embedding_pos": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
                          _c_void_p, _c_void_p],
     "rl_residual_inject": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
@@ -432,11 +451,14 @@ def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, slot_of_token: tor
 def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
                    slot_of_token: torch.Tensor, positions: torch.Tensor, out: torch.Tensor,
                    num_heads: int, num_kv_heads: int, head_dim: int, scale: float, window: int = 0,
-                   value_dim: Optional[int] = None, sink: bool = False, gate: Optional[torch.Tensor] = None) -> None:
+                   value_dim: Optional[int] = None, sink: bool = False, gate: Optional[torch.Tensor] = None,
+                   softcap: float = 0.0, keep_first: int = 0) -> None:
     """q: [M, >= H*hd] (a view into the qkv buffer is fine), out: [M, H*vd] where vd is
     ``value_dim`` (default: head_dim), the width of a value head.  ``sink``: the softmax's
     denominator has one more term of score 0 (and no value).  ``gate`` [M, H*vd] (a view is
-    fine): the output is multiplied by sigmoid(gate) before it is stored."""
+    fine): the output is multiplied by sigmoid(gate) before it is stored.  ``softcap`` > 0: a score s
+    (scale included) becomes softcap * tanh(s / softcap).  ``keep_first``: with a window, positions
+    [0, keep_first) stay visible after the window has passed them."""
     vd = head_dim if value_dim is None else value_dim
     _need(q, "q", contiguous=False); _need(k_pool, "k_pool", q.dtype); _need(v_pool, "v_pool", q.dtype)
     _need(out, "out", q.dtype); _need(page_table, "page_table", torch.int32)
@@ -449,12 +471,203 @@ def attention_simt(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, 
         _need(gate, "gate", q.dtype, contiguous=False)
         assert gate.shape == (M, num_heads * vd) and gate.stride(1) == 1
         ldg = gate.stride(0) if M > 1 else num_heads * vd
-    _check(library().rl_attention_simt_gated(
+    _check(library().rl_attention_simt_masked(
         q.data_ptr(), ldq, k_pool.data_ptr(), v_pool.data_ptr(), _dt(q), page_table.data_ptr(),
         page_table.shape[1], slot_of_token.data_ptr(), positions.data_ptr(), out.data_ptr(), out.stride(0),
-        M, num_heads, num_kv_heads, head_dim, vd, float(scale), int(window), int(bool(sink)), _ptr(gate), ldg, _stream()),
+        M, num_heads, num_kv_heads, head_dim, vd, float(scale), int(window), int(bool(sink)), _ptr(gate), ldg,
+        float(softcap or 0.0), int(keep_first or 0), _stream()),
         "rl_attention_simt")
     _count()
+
+
+# ----------------------------------------------------------------------------- short convolutions, recurrences, fused norms
+def _state_args(state: torch.Tensor):
+    """Pointer and row stride (in floats) of a per-slot state view [slots, nbytes] (uint8; a column range of the
+    cache's state area, so rows are further apart than they are long)."""
+    _need(state, "state", torch.uint8, contiguous=False)
+    assert state.dim() == 2 and state.stride(1) == 1 and state.stride(0) % 4 == 0 and state.data_ptr() % 4 == 0
+    return state.data_ptr(), state.stride(0) // 4
+
+
+def short_conv(u: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], silu: bool, slot_of_token: torch.Tensor,
+               state: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, c] = act(bias[c] + sum_j weight[c, j] * u[t - taps + 1 + j, c]) along each sequence; inputs of earlier
+    steps come from ``state`` (per slot float [taps - 1, C], written by ``short_conv_state`` afterwards)."""
+    _need(u, "u", contiguous=False); _need(weight, "weight", torch.float32); _need(out, "out", u.dtype, contiguous=False)
+    _need(slot_of_token, "slot_of_token", torch.int32)
+    M, C = out.shape
+    taps = weight.shape[1]
+    assert weight.shape == (C, taps) and u.shape == (M, C) and u.stride(1) == 1 and out.stride(1) == 1
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        assert bias.numel() == C
+    sp, ss = _state_args(state)
+    assert state.shape[1] >= 4 * (taps - 1) * C
+    _check(library().rl_short_conv(u.data_ptr(), u.stride(0), _dt(u), weight.data_ptr(), _ptr(bias), int(bool(silu)), C, taps,
+                                   slot_of_token.data_ptr(), sp, ss, out.data_ptr(), out.stride(0), M, _stream()), "rl_short_conv")
+    _count()
+
+
+def short_conv_state(u: torch.Tensor, taps: int, cu_seqlens: torch.Tensor, seq_slots: torch.Tensor, state: torch.Tensor) -> None:
+    """After the step's convolution: every sequence's state takes its last ``taps - 1`` inputs."""
+    _need(u, "u", contiguous=False); _need(cu_seqlens, "cu_seqlens", torch.int32); _need(seq_slots, "seq_slots", torch.int32)
+    M, C = u.shape
+    assert u.stride(1) == 1
+    sp, ss = _state_args(state)
+    assert state.shape[1] >= 4 * (taps - 1) * C
+    if taps <= 1:
+        return
+    _check(library().rl_short_conv_state(u.data_ptr(), u.stride(0), _dt(u), C, int(taps), cu_seqlens.data_ptr(), seq_slots.data_ptr(),
+                                         seq_slots.numel(), sp, ss, _stream()), "rl_short_conv_state")
+    _count()
+
+
+def qkv_prepare(u: torch.Tensor, q_out: torch.Tensor, conv_weight: Optional[torch.Tensor], state: Optional[torch.Tensor],
+                q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float, positions: torch.Tensor,
+                slot_of_token: torch.Tensor, page_table: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, magnitude: float,
+                num_heads: int, num_kv_heads: int, head_dim: int, value_dim: int,
+                k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor]) -> None:
+    """From the projected rows u [M, H*hd + G*hd + G*vd]: a short convolution over time (``conv_weight`` float
+    [C, taps] with its per-slot ``state``), an RMS norm of every query and key head (``q_norm``, ``k_norm`` float
+    [hd]), the rotary encoding of the first ``rotary_dim`` dimensions (half-split pairs, cos and sin times
+    ``magnitude``), queries to ``q_out`` [M, H*hd], keys and values to their pages.  Every stage is optional."""
+    _need(u, "u"); _need(q_out, "q_out", u.dtype); _need(positions, "positions", torch.int32)
+    _need(slot_of_token, "slot_of_token", torch.int32); _need(page_table, "page_table", torch.int32)
+    _need(inv_freq, "inv_freq", torch.float32)
+    M = u.shape[0]
+    C = (num_heads + num_kv_heads) * head_dim + num_kv_heads * value_dim
+    assert u.shape[1] == C and q_out.shape == (M, num_heads * head_dim) and inv_freq.numel() >= max(1, rotary_dim // 2)
+    taps, sp, ss = 0, None, 0
+    if conv_weight is not None:
+        _need(conv_weight, "conv_weight", torch.float32)
+        taps = conv_weight.shape[1]
+        assert conv_weight.shape == (C, taps)
+        if taps > 1:
+            sp, ss = _state_args(state)
+            assert state.shape[1] >= 4 * (taps - 1) * C
+    for t, name in ((q_norm, "q_norm"), (k_norm, "k_norm")):
+        if t is not None:
+            _need(t, name, torch.float32)
+            assert t.numel() == head_dim
+    if k_pool is not None:
+        _need(k_pool, "k_pool", u.dtype); _need(v_pool, "v_pool", u.dtype)
+        assert k_pool.shape[1:] == (num_kv_heads, PAGE_SIZE, head_dim) and v_pool.shape[1:] == (num_kv_heads, PAGE_SIZE, value_dim)
+    _check(library().rl_qkv_prepare(u.data_ptr(), u.stride(0), q_out.data_ptr(), q_out.stride(0), _dt(u), _ptr(conv_weight), taps,
+                                    sp, ss, _ptr(q_norm), _ptr(k_norm), float(eps), positions.data_ptr(), slot_of_token.data_ptr(),
+                                    page_table.data_ptr(), page_table.shape[1], inv_freq.data_ptr(), int(rotary_dim), float(magnitude),
+                                    M, num_heads, num_kv_heads, head_dim, value_dim, _ptr(k_pool), _ptr(v_pool), _stream()),
+           "rl_qkv_prepare")
+    _count()
+
+
+def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, state: torch.Tensor,
+                cu_seqlens: torch.Tensor, seq_slots: torch.Tensor, num_heads: int, heads_per_group: int, dk: int, dv: int,
+                rate: torch.Tensor, dt_raw: Optional[torch.Tensor] = None, dt_bias: Optional[torch.Tensor] = None,
+                skip: Optional[torch.Tensor] = None, silu: bool = False) -> None:
+    """S_t = a_t S_{t-1} + b_t k_t v_t^T, out_t = S_t^T q_t (+ skip[h] v_t) for every head of every sequence of the
+    step, the state (float [H, dv, dk] a slot) read from and left in ``state``.  Without ``dt_raw``: a_t = rate[h],
+    b_t = 1.  With it: dt = softplus(dt_raw[t, h] + dt_bias[h]), a_t = exp(-exp(rate[h]) * dt), b_t = dt.  q, k
+    [M, (H / heads_per_group) * dk], v [M, H * dv] (views are fine), out float32 [M, H * dv].  ``silu``: q, k and v
+    pass through silu first."""
+    for t, name in ((q, "q"), (k, "k"), (v, "v")):
+        _need(t, name, q.dtype, contiguous=False)
+        assert t.stride(1) == 1
+    _need(out, "out", torch.float32); _need(rate, "rate", torch.float32)
+    _need(cu_seqlens, "cu_seqlens", torch.int32); _need(seq_slots, "seq_slots", torch.int32)
+    M = out.shape[0]
+    assert out.shape == (M, num_heads * dv) and rate.numel() == num_heads and num_heads % heads_per_group == 0
+    assert q.shape == (M, num_heads // heads_per_group * dk) and k.shape == q.shape and v.shape == (M, num_heads * dv)
+    mode, lddt = 0, 0
+    if dt_raw is not None:
+        _need(dt_raw, "dt_raw", q.dtype, contiguous=False); _need(dt_bias, "dt_bias", torch.float32)
+        assert dt_raw.shape == (M, num_heads) and dt_raw.stride(1) == 1 and dt_bias.numel() == num_heads
+        mode, lddt = 1, dt_raw.stride(0)
+    if skip is not None:
+        _need(skip, "skip", torch.float32)
+        assert skip.numel() == num_heads
+    sp, ss = _state_args(state)
+    assert state.shape[1] >= 4 * num_heads * dk * dv
+    _check(library().rl_linear_scan(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), _ptr(dt_raw), lddt,
+                                    _dt(q), _ptr(dt_bias), rate.data_ptr(), _ptr(skip), mode, int(bool(silu)), cu_seqlens.data_ptr(),
+                                    seq_slots.data_ptr(), seq_slots.numel(), sp, ss, out.data_ptr(), out.stride(0), num_heads,
+                                    heads_per_group, dk, dv, _stream()), "rl_linear_scan")
+    _count()
+
+
+def norm_add(x: torch.Tensor, y0: torch.Tensor, s0: float, y1: Optional[torch.Tensor], s1: float, weight: torch.Tensor, eps: float,
+             x_bf16: Optional[torch.Tensor] = None) -> None:
+    """x += rms_norm(s0 * y0 + s1 * y1) * weight, all float32 [M, d] (``y1`` may be ``None``); ``x_bf16``: also
+    leave the new x there, rounded."""
+    _need(x, "x", torch.float32); _need(y0, "y0", torch.float32); _need(weight, "weight", torch.float32)
+    M, d = x.shape
+    assert y0.shape == (M, d) and weight.numel() == d
+    if y1 is not None:
+        _need(y1, "y1", torch.float32)
+        assert y1.shape == (M, d)
+    if x_bf16 is not None:
+        _need(x_bf16, "x_bf16", torch.bfloat16)
+        assert x_bf16.shape == (M, d)
+    _check(library().rl_norm_add(x.data_ptr(), y0.data_ptr(), float(s0), _ptr(y1), float(s1), weight.data_ptr(), float(eps), M, d,
+                                 _ptr(x_bf16), _stream()), "rl_norm_add")
+    _count()
+
+
+def gated_norm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, groups: int = 1,
+               gate_act: str = "silu", gate_first: bool = True) -> None:
+    """``gate_first``: out = rms_norm_in_groups(y * act(gate)) * weight; else out = rms_norm(y) * weight * act(gate).
+    y float32 [M, n]; gate and out [M, n] in the compute dtype (views are fine); the norm runs over ``groups``
+    equal parts of a row, each by its own root mean square."""
+    _need(y, "y", torch.float32, contiguous=False); _need(gate, "gate", out.dtype, contiguous=False)
+    _need(out, "out", contiguous=False); _need(weight, "weight", torch.float32)
+    M, n = y.shape
+    assert gate.shape == (M, n) and out.shape == (M, n) and weight.numel() == n and n % groups == 0
+    assert y.stride(1) == 1 and gate.stride(1) == 1 and out.stride(1) == 1
+    act = {"silu": 0, "sigmoid": 1}[gate_act]
+    _check(library().rl_gated_norm(y.data_ptr(), y.stride(0), gate.data_ptr(), gate.stride(0), _dt(out), act, int(bool(gate_first)),
+                                   weight.data_ptr(), float(eps), M, groups, n // groups, out.data_ptr(), out.stride(0), _stream()),
+           "rl_gated_norm")
+    _count()
+
+
+def gelu_gate(t: torch.Tensor, tokens: torch.Tensor, table: torch.Tensor, col0: int, out: torch.Tensor) -> None:
+    """out[m, i] = gelu_tanh(t[m, i]) * table[tokens[m], col0 + i]."""
+    _need(t, "t"); _need(tokens, "tokens", torch.int32); _need(table, "table", t.dtype); _need(out, "out", t.dtype)
+    M, n = t.shape
+    assert out.shape == (M, n) and tokens.numel() == M and 0 <= col0 and col0 + n <= table.shape[1]
+    _check(library().rl_gelu_gate(t.data_ptr(), t.stride(0), tokens.data_ptr(), table.data_ptr(), table.stride(0), int(col0), n, _dt(t),
+                                  out.data_ptr(), out.stride(0), M, _stream()), "rl_gelu_gate")
+    _count()
+
+
+def moe_route_sigmoid(x: torch.Tensor, router: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int, keep: int,
+                      ids: torch.Tensor, weights: torch.Tensor) -> None:
+    """Router with sigmoid scores: s = sigmoid(router @ x[m]) in 32-bit; experts are chosen by s + correction among
+    the ``keep`` best of ``groups`` groups of neighbours (a group's score: its two largest choice scores); the
+    weights are the chosen experts' s as they are."""
+    _need(x, "x", contiguous=False); _need(router, "router", x.dtype); _need(ids, "ids", torch.int32)
+    _need(weights, "weights", torch.float32)
+    M, d = x.shape
+    E = router.shape[0]
+    assert router.shape == (E, d) and ids.shape == (M, top) and weights.shape == (M, top) and x.stride(1) == 1
+    if correction is not None:
+        _need(correction, "correction", torch.float32)
+        assert correction.numel() == E
+    _check(library().rl_moe_route_sigmoid(x.data_ptr(), x.stride(0) if M > 1 else d, router.data_ptr(), _ptr(correction), _dt(x), M, d,
+                                          E, int(top), int(groups), int(keep), ids.data_ptr(), weights.data_ptr(), _stream()),
+           "rl_moe_route_sigmoid")
+    _count()
+
+
+def moe_select_sigmoid(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int, keep: int,
+                       ids: torch.Tensor, weights: torch.Tensor) -> None:
+    """``moe_route_sigmoid``'s second half alone, from float32 logits [M, E]."""
+    _need(logits, "logits", torch.float32); _need(ids, "ids", torch.int32); _need(weights, "weights", torch.float32)
+    M, E = logits.shape
+    assert ids.shape == (M, top) and weights.shape == (M, top)
+    _check(library().rl_moe_select_sigmoid(logits.data_ptr(), M, E, int(top), _ptr(correction), int(groups), int(keep), ids.data_ptr(),
+                                           weights.data_ptr(), _stream()), "rl_moe_select_sigmoid")
+    _count()
+
 
 
 def repeat_penalty(logits: torch.Tensor, recent: torch.Tensor, recent_len: torch.Tensor, penalty: float) -> None:
@@ -929,16 +1142,18 @@ def attention_prefill_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
 def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
               step, out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
               window: int = 0, value_dim: Optional[int] = None, sink: bool = False,
-              gate: Optional[torch.Tensor] = None) -> None:
+              gate: Optional[torch.Tensor] = None, softcap: float = 0.0, keep_first: int = 0) -> None:
     """Attention of the step's tokens over the cache; picks the kernel for the
     dtype and the shape of the step.  ``step`` carries positions, slots and
     sequence boundaries (engine.step.StepState).  Value heads of another width than the
     key heads (``value_dim``) run on the any-shape kernel; the tensor-core kernels take
     one width for both.  ``sink``: one more term of score 0 in the softmax's denominator.
     ``gate`` [M, H*vd]: the output is multiplied by sigmoid(gate)."""
-    if value_dim is not None and value_dim != head_dim:
+    if (value_dim is not None and value_dim != head_dim) or softcap or (keep_first and window):
+        # soft-capped scores and kept first tokens exist in the any-shape kernel only
         attention_simt(q, k_pool, v_pool, page_table, step.slot_of_token, step.positions, out,
-                       num_heads, num_kv_heads, head_dim, scale, window, value_dim=value_dim, sink=sink, gate=gate)
+                       num_heads, num_kv_heads, head_dim, scale, window, value_dim=value_dim, sink=sink, gate=gate,
+                       softcap=softcap, keep_first=keep_first)
         return
     if step.is_decode and attention_decode_supported(q.dtype, num_heads, num_kv_heads, head_dim):
         splits = decode_splits(q.shape[0], num_kv_heads)

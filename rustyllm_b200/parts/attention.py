@@ -8,7 +8,12 @@ x += Wo attn.  Options other designs use, each a constructor parameter: another 
 scale than 1/sqrt(head_dim) (``scale``); a sliding ``window`` (a query at position i reads
 positions j with 0 <= i - j < window); a ``sink`` (the softmax's denominator has one more
 term, of score 0 and without a value: p_j = e^{s_j} / (1 + sum_t e^{s_t})); an output gate
-(``names["g"]``: the concatenated heads are multiplied by sigmoid(Wg xn) before Wo).  Here Wq, Wk, Wv are one matrix [(H + 2G) hd x d] so that one product
+(``names["g"]``: the concatenated heads are multiplied by sigmoid(Wg xn) before Wo); a short causal
+convolution over time on every channel of q, k and v, directly behind the projection (``conv_taps``; the
+last taps - 1 projected rows of a sequence are per-sequence state); an RMS norm of every query and key head
+with one weight vector for all heads, before the rotation (``names["q_norm"]``, ``names["k_norm"]``,
+``qk_norm_eps``); scores squashed to softcap * tanh(s / softcap) (``softcap``); first positions that stay
+visible behind a window (``keep_first``).  Here Wq, Wk, Wv are one matrix [(H + 2G) hd x d] so that one product
 serves all three, rotation and cache write are one kernel, and all tokens of the
 step (several sequences, prompt or single tokens) run together.
 """
@@ -20,10 +25,10 @@ from typing import Dict, Optional
 import torch
 
 from .. import kernels as K
-from ..cache.sequence_cache import KVNeed
+from ..cache.sequence_cache import KVNeed, StateNeed
 from ..config.spec import ParamSource, ParamSpec, PartSpec
 from .base import Mixer, NormedInput, Runtime
-from .linear import OUT_ADD_F32, OUT_SAME, can_fold_norms, linear
+from .linear import OUT_ADD_F32, OUT_F32, OUT_SAME, can_fold_norms, linear
 from .registry import build_part, register_mixer
 
 
@@ -32,7 +37,9 @@ class GQAttention(Mixer):
     def __init__(self, runtime: Runtime, hidden_size: int, num_heads: int, num_kv_heads: int,
                  head_dim: int, position: PartSpec, names: Dict[str, str], bias: bool = False,
                  window: Optional[int] = None, value_dim: Optional[int] = None,
-                 scale: Optional[float] = None, sink: bool = False):
+                 scale: Optional[float] = None, sink: bool = False, conv_taps: int = 0,
+                 qk_norm_eps: Optional[float] = None, softcap: Optional[float] = None, keep_first: int = 0,
+                 bias_o: Optional[bool] = None):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads are no multiple of {num_kv_heads} KV heads")
         if head_dim % 2 or not (0 < head_dim <= 256):
@@ -55,6 +62,24 @@ class GQAttention(Mixer):
         self.gated = "g" in names          # an output gate: its rows ride behind q, k, v in the one product
         self.position = build_part("position", position, runtime)
         self.wqkv = self.wo = self.bqkv = self.bo = None
+        if conv_taps < 0 or conv_taps > 8:
+            raise ValueError(f"conv_taps {conv_taps} outside [0, 8]")
+        self.conv_taps = int(conv_taps)                      # 0: no convolution (1 would be a gain a channel)
+        self.qk_norm = "q_norm" in names or "k_norm" in names
+        if self.qk_norm and qk_norm_eps is None:
+            raise ValueError("query and key norms need qk_norm_eps")
+        self.qk_norm_eps = 0.0 if qk_norm_eps is None else float(qk_norm_eps)
+        if softcap is not None and not softcap > 0:
+            raise ValueError(f"softcap {softcap} must be > 0 or None")
+        self.softcap = 0.0 if softcap is None else float(softcap)
+        if keep_first < 0:
+            raise ValueError("keep_first must be >= 0")
+        self.keep_first = int(keep_first) if window is not None else 0
+        self.bias_o = bias if bias_o is None else bool(bias_o)
+        if self.gated and (self.conv_taps or self.qk_norm):
+            raise ValueError("an output gate together with a convolution or head norms is not built")
+        self.channels = (num_heads + num_kv_heads) * head_dim + num_kv_heads * vd
+        self.conv_w = self.q_norm_w = self.k_norm_w = None
 
     def param_specs(self) -> Dict[str, ParamSpec]:
         d, H, G, hd, vd, n = self.d, self.H, self.G, self.hd, self.vd, self.names
@@ -64,22 +89,43 @@ class GQAttention(Mixer):
         if self.gated:
             qkv += (ParamSource(n["g"] + sfx, (H * vd, d)),)
         specs = {"wqkv": ParamSpec(qkv), "wo": ParamSpec((ParamSource(n["o"] + sfx, (d, H * vd)),))}
+        bsfx = n.get("bias_suffix", ".bias")
         if self.bias:
-            specs["bqkv"] = ParamSpec((ParamSource(n["q"] + ".bias", (H * hd,)),
-                                       ParamSource(n["k"] + ".bias", (G * hd,)),
-                                       ParamSource(n["v"] + ".bias", (G * vd,))), role="vector")
-            specs["bo"] = ParamSpec((ParamSource(n["o"] + ".bias", (d,)),), role="vector")
+            specs["bqkv"] = ParamSpec((ParamSource(n["q"] + bsfx, (H * hd,)),
+                                       ParamSource(n["k"] + bsfx, (G * hd,)),
+                                       ParamSource(n["v"] + bsfx, (G * vd,))), role="vector")
+        if self.bias_o:
+            specs["bo"] = ParamSpec((ParamSource(n["o"] + bsfx, (d,)),), role="vector")
+        if self.conv_taps:
+            csfx, t = n.get("conv_suffix", ".conv"), self.conv_taps
+            specs["conv_w"] = ParamSpec((ParamSource(n["q"] + csfx, (H * hd, t)), ParamSource(n["k"] + csfx, (G * hd, t)),
+                                         ParamSource(n["v"] + csfx, (G * vd, t))), role="vector")
+        if "q_norm" in n:
+            specs["q_norm_w"] = ParamSpec((ParamSource(n["q_norm"], (hd,)),), role="vector", init="ones")
+        if "k_norm" in n:
+            specs["k_norm_w"] = ParamSpec((ParamSource(n["k_norm"], (hd,)),), role="vector", init="ones")
         return specs
 
     def kv_need(self) -> KVNeed:
-        return KVNeed(self.G, self.hd, self.window, None if self.vd == self.hd else self.vd)
+        return KVNeed(self.G, self.hd, self.window, None if self.vd == self.hd else self.vd, self.keep_first)
+
+    def state_need(self) -> Optional[StateNeed]:
+        # the last taps - 1 projected rows of a sequence, float32
+        return StateNeed(4 * (self.conv_taps - 1) * self.channels) if self.conv_taps > 1 else None
 
     folds_norms = True
 
     def takes_normed_input(self, num_tokens: int) -> bool:
         return can_fold_norms(self.wqkv, self.runtime.compute_dtype, num_tokens)
 
-    def forward(self, xn, residual: torch.Tensor, step, cache, then_norm=None):
+    def forward_out(self, xn, step, cache):
+        """The mixer's output as float32 [M, d] of its own (for a block that norms it before it joins the stream):
+        a list of (tensor, factor) terms."""
+        y = torch.empty((xn.shape[0], self.d), dtype=torch.float32, device=xn.device)
+        self.forward(xn, y, step, cache, _out_mode=OUT_F32)
+        return [(y, 1.0)]
+
+    def forward(self, xn, residual: torch.Tensor, step, cache, then_norm=None, _out_mode=OUT_ADD_F32):
         H, G, hd, vd = self.H, self.G, self.hd, self.vd
         M = xn.shape[0]
         dt = xn.dtype
@@ -89,7 +135,21 @@ class GQAttention(Mixer):
         k_pool, v_pool = group.k_pool(layer), group.v_pool(layer)
         pos = self.position
         x = xn.weighted if isinstance(xn, NormedInput) else xn
-        if (dt == torch.bfloat16 and vd == hd and not self.gated and self.wqkv.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16
+        prepared = self.conv_taps or self.qk_norm or pos.magnitude != 1.0
+        q = qkv
+        if prepared:
+            # convolution, head norms, rotation and the cache write in one kernel behind the product
+            linear(xn, self.wqkv, qkv, OUT_SAME, self.bqkv)
+            q = torch.empty((M, H * hd), dtype=dt, device=xn.device)
+            if pos.interleaved:
+                raise K.KernelError("interleaved rotary pairs behind a convolution or head norms are not built")
+            K.qkv_prepare(qkv, q, self.conv_w if self.conv_taps else None, cache.state if self.conv_taps > 1 else None,
+                          self.q_norm_w, self.k_norm_w, self.qk_norm_eps, step.positions, step.slot_of_token, group.page_table,
+                          pos.inv_freq, pos.rotary_dim, pos.magnitude, H, G, hd, vd,
+                          k_pool if cache.writes else None, v_pool if cache.writes else None)
+            if self.conv_taps > 1 and cache.writes:
+                K.short_conv_state(qkv, self.conv_taps, step.cu_seqlens, step.seq_slots, cache.state)
+        elif (dt == torch.bfloat16 and vd == hd and not self.gated and self.wqkv.dtype == torch.bfloat16 and k_pool.dtype == torch.bfloat16
                 and K.gemm_tc_qkv_rope_supported(x, self.wqkv, H, G, hd, pos.rotary_dim)):
             # few tokens: rotation and cache write ride in the product's epilogue
             kw = dict(row_sumsq=xn.sumsq, row_eps=xn.eps) if isinstance(xn, NormedInput) else {}
@@ -102,6 +162,7 @@ class GQAttention(Mixer):
                             pos.rotary_dim, pos.interleaved,
                             k_pool if cache.writes else None, v_pool if cache.writes else None, value_dim=vd)
         attn = torch.empty((M, H * vd), dtype=dt, device=xn.device)
-        K.attention(qkv, k_pool, v_pool, group.page_table, step, attn, H, G, hd, self.scale,
-                    self.window or 0, value_dim=vd, sink=self.sink, gate=qkv[:, n_qkv:] if self.gated else None)
-        return linear(attn, self.wo, residual, OUT_ADD_F32, self.bo, then_norm=then_norm)
+        K.attention(q, k_pool, v_pool, group.page_table, step, attn, H, G, hd, self.scale,
+                    self.window or 0, value_dim=vd, sink=self.sink, gate=qkv[:, n_qkv:] if self.gated else None,
+                    softcap=self.softcap, keep_first=self.keep_first)
+        return linear(attn, self.wo, residual, _out_mode, self.bo, then_norm=then_norm)

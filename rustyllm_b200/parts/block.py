@@ -53,3 +53,81 @@ class PreNormBlock(Block):
             return self.feed_forward.forward(xn2, x, step, then_norm=next_norm)
         self.feed_forward.forward(xn2, x, step)
         return None
+
+
+@register_block("post_norm")
+class PostNormBlock(Block):
+    """A layer whose sublayers read the stream itself and whose norms sit on what they return:
+
+        x += norm1(mixer(x));  x += norm2(feed_forward(x));  then, where the layer has one, ``after`` (a part of
+        role "inject", e.g. a per-token side input) changes x once more.
+
+    The stream is float32; a bfloat16 run hands the sublayers its rounding, which the kernel that adds a normed
+    output into the stream leaves behind for the next reader.  A mixer that offers ``forward_out`` returns its
+    output as float32 terms (tensor, factor) - mixers side by side return two - and the sum, the norm and the
+    addition are one kernel; any other part adds into a zeroed buffer.
+    """
+
+    def __init__(self, runtime: Runtime, mixer: Mixer, mixer_norm: Norm, feed_forward: FeedForward,
+                 feed_forward_norm: Norm, after=None):
+        from .registry import build_part
+        self.runtime = runtime
+        self.mixer, self.mixer_norm = mixer, mixer_norm
+        self.feed_forward, self.feed_forward_norm = feed_forward, feed_forward_norm
+        self.after = build_part("inject", after, runtime) if after is not None else None
+        if not hasattr(mixer_norm, "eps") or not (getattr(feed_forward, "absent", False) or hasattr(feed_forward_norm, "eps")):
+            raise ValueError("a post_norm block needs RMS norms (a weight and an eps)")
+
+    def sub_parts(self):
+        parts = {"mixer": self.mixer, "mixer_norm": self.mixer_norm,
+                 "feed_forward": self.feed_forward, "feed_forward_norm": self.feed_forward_norm}
+        if self.after is not None:
+            parts["after"] = self.after
+        return parts
+
+    def _input(self, x: torch.Tensor, rounded):
+        """What a sublayer reads: x itself in a 32-bit run, its bfloat16 rounding otherwise."""
+        if self.runtime.compute_dtype == torch.float32:
+            return x
+        if rounded is not None:
+            return rounded
+        from .. import kernels as K
+        h = torch.empty(x.shape, dtype=self.runtime.compute_dtype, device=x.device)
+        K.convert(x, h)
+        return h
+
+    def _join(self, x, terms, norm):
+        """x += norm(sum of factor * tensor); returns the new x's bfloat16 rounding in a bfloat16 run."""
+        from .. import kernels as K
+        if len(terms) > 2:
+            raise K.KernelError("more than two terms under one norm are not built")
+        rounded = None
+        if self.runtime.compute_dtype == torch.bfloat16:
+            rounded = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+        (y0, s0), (y1, s1) = terms[0], (terms[1] if len(terms) > 1 else (None, 0.0))
+        K.norm_add(x, y0, s0, y1, s1, norm.weight, norm.eps, rounded)
+        return rounded
+
+    def forward(self, x: torch.Tensor, step, cache, pending=None, next_norm=None):
+        h = self._input(x, getattr(step, "derived", {}).pop(("stream_rounded", id(x)), None))
+        if hasattr(self.mixer, "forward_out"):
+            terms = self.mixer.forward_out(h, step, cache)
+        else:
+            y = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+            self.mixer.forward(h, y, step, cache)
+            terms = [(y, 1.0)]
+        rounded = self._join(x, terms, self.mixer_norm)
+        if not getattr(self.feed_forward, "absent", False):
+            h = self._input(x, rounded)
+            if hasattr(self.feed_forward, "forward_out"):
+                terms = self.feed_forward.forward_out(h, step)
+            else:
+                y = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+                self.feed_forward.forward(h, y, step)
+                terms = [(y, 1.0)]
+            rounded = self._join(x, terms, self.feed_forward_norm)
+        if self.after is not None:
+            rounded = self.after.forward(x, None, step, rounded=self._input(x, rounded))
+        if rounded is not None and hasattr(step, "derived"):
+            step.derived[("stream_rounded", id(x))] = rounded      # the next layer's first reader takes it
+        return None

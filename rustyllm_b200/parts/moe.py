@@ -29,7 +29,8 @@ from .registry import build_part, register_feed_forward
 @register_feed_forward("moe_mlp")
 class MoEMLP(FeedForward):
     def __init__(self, runtime: Runtime, hidden_size: int, expert_size: int, num_experts: int, top: int,
-                 names: Dict[str, str], router_bias: bool = True, shared: Optional[PartSpec] = None):
+                 names: Dict[str, str], router_bias: bool = True, shared: Optional[PartSpec] = None,
+                 scoring: str = "softmax", groups: int = 1, keep_groups: int = 1):
         """``names``: "router" (the router's matrix; its bias is that name + ``names["bias_suffix"]``),
         "expert" (a format string with ``{e}`` for the expert's number, giving the prefix of its
         "gate", "up" and "down" tensors), "suffix" (what follows a projection's name)."""
@@ -37,6 +38,22 @@ class MoEMLP(FeedForward):
             raise ValueError(f"top {top} must lie in [1, {num_experts}]")
         if top > 32:
             raise ValueError("at most 32 experts a token")
+        if scoring not in ("softmax", "sigmoid"):
+            raise ValueError(f"scoring {scoring!r} is not known; known: 'softmax', 'sigmoid'")
+        # "sigmoid": scores s = sigmoid(z); experts are chosen by s + correction (``names["correction"]``, a value an
+        # expert) among the ``keep_groups`` best of ``groups`` equal groups of neighbours (a group's score: its two
+        # largest choice scores); the weights are the chosen experts' s, not renormalised
+        self.scoring, self.groups, self.keep_groups = scoring, int(groups), int(keep_groups)
+        if scoring == "sigmoid":
+            if router_bias:
+                raise ValueError("a router with sigmoid scores has a correction of the choice, not a bias")
+            if groups < 1 or num_experts % groups or not (1 <= keep_groups <= groups):
+                raise ValueError(f"{groups} groups (keep {keep_groups}) do not fit {num_experts} experts")
+            if keep_groups * (num_experts // groups) < top:
+                raise ValueError(f"{keep_groups} groups of {num_experts // groups} experts hold fewer than top = {top}")
+        elif groups != 1:
+            raise ValueError("groups of experts exist with sigmoid scoring only")
+        self.correction = None
         self.runtime = runtime
         self.d, self.F, self.E, self.top = hidden_size, expert_size, num_experts, top
         self.names = names
@@ -58,6 +75,8 @@ class MoEMLP(FeedForward):
             "wgu": ParamSpec(gu),                                                   # [E * 2 * F, d], see ``bind``
             "wdown": ParamSpec(tuple(ParamSource(p + ".down" + sfx, (d, F)) for p in ex)),   # [E * d, F]
         }
+        if self.scoring == "sigmoid" and "correction" in n:
+            specs["correction"] = ParamSpec((ParamSource(n["correction"], (E,)),), role="vector", init="zeros")
         if self.router_bias:
             specs["router_b"] = ParamSpec((ParamSource(n["router"] + n.get("bias_suffix", ".bias"), (E,)),),
                                           role="vector", init="zeros")
@@ -84,7 +103,14 @@ class MoEMLP(FeedForward):
         router = self.router
         if router.dtype != xn.dtype:
             raise K.KernelError(f"the router's matrix is {router.dtype} in a {xn.dtype} run")
-        if M >= self.ROUTER_PRODUCT_FROM and self.E <= 1024:
+        if self.scoring == "sigmoid":
+            if M >= self.ROUTER_PRODUCT_FROM:
+                logits = torch.empty((M, self.E), dtype=torch.float32, device=xn.device)
+                linear(xn, router, logits, OUT_F32)
+                K.moe_select_sigmoid(logits, self.correction, self.top, self.groups, self.keep_groups, ids, weights)
+            else:
+                K.moe_route_sigmoid(xn, router, self.correction, self.top, self.groups, self.keep_groups, ids, weights)
+        elif M >= self.ROUTER_PRODUCT_FROM and self.E <= 1024:
             # many tokens: the logits as one matrix product (32-bit accumulation, the bias in its epilogue)
             logits = torch.empty((M, self.E), dtype=torch.float32, device=xn.device)
             linear(xn, router, logits, OUT_F32, self.router_b)

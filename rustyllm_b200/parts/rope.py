@@ -59,6 +59,7 @@ class RotaryEmbedding(PositionEncoding):
         self.head_dim = head_dim
         self.rotary_dim = rotary_dim
         self.interleaved = pairing == "interleaved"
+        self.magnitude = 1.0          # factor on every cosine and sine (kinds that stretch the context set it)
         inv = rope_inverse_frequencies(theta, rotary_dim, scaling) if rotary_dim else torch.zeros(1)
         self.inv_freq = inv.to(runtime.device)
 
@@ -69,3 +70,39 @@ class NoPositionEncoding(RotaryEmbedding):
 
     def __init__(self, runtime: Runtime, head_dim: int):
         super().__init__(runtime, head_dim=head_dim, rotary_dim=0, theta=1.0)
+
+
+def yarn_inverse_frequencies(base: float, rotary_dim: int, factor: float, original: float, fast: float, slow: float) -> torch.Tensor:
+    """Frequencies of a context stretched by ``factor`` beyond ``original`` positions: pair i turns at
+    f_i = base^(-2i/r).  dim(t) = r ln(original / (2 pi t)) / (2 ln base) is the (real-valued) pair that makes t
+    turns over the original context; pairs up to lo = floor(dim(fast)) keep f_i, pairs from hi = ceil(dim(slow))
+    on turn at f_i / factor, and between the two the blend is linear in i."""
+    half = rotary_dim // 2
+
+    def pair_of(turns: float) -> float:
+        return rotary_dim * math.log(original / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+    lo = max(math.floor(pair_of(fast)), 0)
+    hi = min(math.ceil(pair_of(slow)), rotary_dim - 1)
+    inv = []
+    for i in range(half):
+        f = base ** (-2.0 * i / rotary_dim)
+        ramp = min(1.0, max(0.0, (i - lo) / max(hi - lo, 0.001)))
+        inv.append(f / factor * ramp + f * (1.0 - ramp))
+    return torch.tensor(inv, dtype=torch.float64).to(torch.float32)
+
+
+@register_position("rope_yarn")
+class YarnRotaryEmbedding(RotaryEmbedding):
+    """Half-split rotary pairs over the first ``rotary_dim`` dimensions with the stretched frequencies above;
+    every cosine and sine is multiplied by 0.1 ln(factor) + 1.  Without ``factor`` (or with factor 1): the plain
+    frequencies and magnitude 1."""
+
+    def __init__(self, runtime: Runtime, head_dim: int, rotary_dim: int, base: float, factor: Optional[float] = None,
+                 original: Optional[float] = None, fast: Optional[float] = None, slow: Optional[float] = None):
+        super().__init__(runtime, head_dim=head_dim, rotary_dim=rotary_dim, theta=base)
+        if factor is not None and rotary_dim:
+            if not (factor >= 1.0 and original and fast and slow):
+                raise ValueError("a stretched rotary encoding needs factor >= 1, original, fast and slow")
+            self.inv_freq = yarn_inverse_frequencies(base, rotary_dim, float(factor), float(original), float(fast),
+                                                     float(slow)).to(runtime.device)
+            self.magnitude = 0.1 * math.log(float(factor)) + 1.0

@@ -80,6 +80,18 @@ def place_source(dest: torch.Tensor, ps: ParamSpec, index: int, tensor: torch.Te
         dest[row:row + ps.sources[index].shape[0]].copy_(tensor)
 
 
+def shares_storage(params: Mapping[str, ParamSpec], ps: ParamSpec, present: Sequence[bool]) -> bool:
+    """Whether a parameter takes another's storage instead of a copy of its own: a tied parameter none of
+    whose tensors the file holds, or one that names as ``alias_of`` a parameter reading the very same tensors
+    (a table several parts share)."""
+    if ps.alias_of is None:
+        return False
+    if not any(present):
+        return True
+    target = params.get(ps.alias_of)
+    return target is not None and target.alias_of is None and target.sources == ps.sources and target.layout == ps.layout
+
+
 def check_checkpoint(params: Mapping[str, ParamSpec], entries: Mapping[str, object],
                      ignored: Iterable[str] = (), where: str = "") -> None:
     """Compare names, shapes and dtype classes; raise one WeightsError for all faults."""
@@ -89,8 +101,8 @@ def check_checkpoint(params: Mapping[str, ParamSpec], entries: Mapping[str, obje
     used = set()
     for path, ps in params.items():
         present = [s.name in entries for s in ps.sources]
-        if ps.alias_of is not None and not any(present):
-            continue  # tied: shares another parameter's storage
+        if shares_storage(params, ps, present):
+            continue  # shares another parameter's storage
         if ps.optional_in_file and not any(present):
             continue
         for s, here in zip(ps.sources, present):
@@ -122,9 +134,10 @@ def load_parameters(params: Mapping[str, ParamSpec], checkpoint: Checkpoint,
     aliases: List[Tuple[str, str]] = []
     for path, ps in params.items():
         present = [s.name in checkpoint.entries for s in ps.sources]
+        if shares_storage(params, ps, present):
+            aliases.append((path, ps.alias_of))
+            continue
         if not any(present):
-            if ps.alias_of is not None:
-                aliases.append((path, ps.alias_of))
             continue
         file_dtypes = {checkpoint.entries[s.name].dtype for s in ps.sources}
         widest = torch.float32 if (torch.float32 in file_dtypes or torch.float64 in file_dtypes) \
