@@ -19,8 +19,8 @@ HBM; no extra flush is needed.
 
     python bench.py --designs
 
-is another program under the same name: prompt and single-token throughput of the Mosurax design beside
-the Llama decoder at two layer sizes of real models (``rustyllm_b200/bench_designs.py``), one JSON line a
+is another program under the same name: prompt and single-token throughput of the Mosurax and Mogutar designs
+beside the Llama decoder at two layer sizes of real models (``rustyllm_b200/bench_designs.py``), one JSON line a
 model and one with the ratios a size.  The headline workload above and its one line are untouched by it.
 """
 import argparse

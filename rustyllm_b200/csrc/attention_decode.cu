@@ -192,6 +192,11 @@ struct DecFinish {
   int sink;
   const __nv_bfloat16* gate;
   int ldg;
+  // not of the finish, but options of the key loop that travel with it: scores squashed to
+  // softcap * tanh(score / softcap) (0: as they are), and positions [0, keep_first) that stay visible
+  // in front of a window
+  float softcap;
+  int keep_first;
 };
 
 __device__ __forceinline__ float dec_finish(float O, float L, float M, const DecFinish& f, int b, int col) {
@@ -256,12 +261,17 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
   float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
 
   // ---- this split's blocks of 16 keys, dealt to the warps in turn ----
+  // The blocks are walked as `num_blk` places: first the blocks that hold kept first tokens and lie wholly in
+  // front of the window's first block, then the window's.  (A plan counts the window's blocks alone: it sets
+  // how many chunks a sequence gets, not what they cover.)
   const int first_blk = start / DEC_BLOCK;
-  const int num_blk = (len + DEC_BLOCK - 1) / DEC_BLOCK - first_blk;
+  const int kept_blk = min((fin.keep_first + DEC_BLOCK - 1) / DEC_BLOCK, first_blk);
+  const int num_blk = (len + DEC_BLOCK - 1) / DEC_BLOCK - first_blk + kept_blk;
   const int rounds = (num_blk + DEC_WARPS - 1) / DEC_WARPS;
   const int per_split = (rounds + num_splits - 1) / num_splits * DEC_WARPS;   // whole rounds: every warp gets a block of each
-  const int blk_lo = first_blk + split * per_split;
-  const int blk_hi = min(blk_lo + per_split, first_blk + num_blk);
+  const int blk_lo = split * per_split;                                      // places
+  const int blk_hi = min(blk_lo + per_split, num_blk);
+  auto block_of = [&](int place) { return place < kept_blk ? place : first_blk + (place - kept_blk); };
   const size_t page_stride = (size_t)G * RL_PAGE * HD;
   const size_t head_off = (size_t)gkv * RL_PAGE * HD;
 
@@ -297,13 +307,13 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
 #pragma unroll
     for (int st = 0; st < DEC_STAGES - 1; ++st) {
       const int pre = blk_lo + warp + st * DEC_WARPS;
-      first_pages[st] = pre < blk_hi ? __ldg(&pages[pre * DEC_BLOCK / RL_PAGE]) : 0;
+      first_pages[st] = pre < blk_hi ? __ldg(&pages[block_of(pre) * DEC_BLOCK / RL_PAGE]) : 0;
     }
     rl_pdl_wait();
 #pragma unroll
     for (int st = 0; st < DEC_STAGES - 1; ++st) {
       const int pre = blk_lo + warp + st * DEC_WARPS;
-      if (pre < blk_hi) issue(pre, st, first_pages[st]);
+      if (pre < blk_hi) issue(block_of(pre), st, first_pages[st]);
       dec_commit();
     }
   }
@@ -323,12 +333,17 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
   }
 
   int it = 0;
-  for (int blk = blk_lo + warp; blk < blk_hi; blk += DEC_WARPS, ++it) {
-    const int key0 = blk * DEC_BLOCK;
+  const float cap_in = fin.softcap > 0.f ? 0.6931471805599453f / fin.softcap : 0.f;      // exp2 domain -> score / softcap
+  const float cap_out = fin.softcap * 1.4426950408889634f;
+  for (int place = blk_lo + warp; place < blk_hi; place += DEC_WARPS, ++it) {
+    const int key0 = block_of(place) * DEC_BLOCK;
     const int st = it % DEC_STAGES;
     {
-      const int ahead = blk + (DEC_STAGES - 1) * DEC_WARPS;
-      if (ahead < blk_hi) issue(ahead, (it + DEC_STAGES - 1) % DEC_STAGES, __ldg(&pages[ahead * DEC_BLOCK / RL_PAGE]));
+      const int ahead = place + (DEC_STAGES - 1) * DEC_WARPS;
+      if (ahead < blk_hi) {
+        const int ab = block_of(ahead);
+        issue(ab, (it + DEC_STAGES - 1) % DEC_STAGES, __ldg(&pages[ab * DEC_BLOCK / RL_PAGE]));
+      }
       dec_commit();
     }
     dec_wait<DEC_STAGES - 1>();     // this lane's pieces of block `blk` have landed,
@@ -354,7 +369,9 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const __nv
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int key = key0 + 8 * nt + 2 * t + (e & 1);
-        s[nt][e] = (key < len && key >= start) ? s[nt][e] * scale_log2e : -INFINITY;
+        float sc = s[nt][e] * scale_log2e;
+        if (fin.softcap > 0.f) sc = cap_out * tanhf(sc * cap_in);
+        s[nt][e] = (key < len && (key >= start || key < fin.keep_first)) ? sc : -INFINITY;
       }
     // streaming softmax for rows g (e = 0, 1) and g + 8 (e = 2, 3)
     uint32_t pa[4];
@@ -653,14 +670,17 @@ extern "C" int rl_attention_decode_order(const int* seq_slots, const int* kv_len
 //
 // sink != 0: the softmax's denominator has one more term, of score 0 and without a value.  gate (may be
 // null): bf16 [num_seqs, ldg]; head h's output is multiplied element by element with
-// sigmoid(gate[b, h*head_dim + i]) before it is stored.
-extern "C" int rl_attention_decode_gated(const void* q, int ldq, const void* k_pool, const void* v_pool,
-                                         const int* page_table, int max_pages, const int* seq_slots, const int* kv_lens,
-                                         void* out, int ldo, float* scratch, const int* plan, int num_seqs, int num_heads,
-                                         int num_kv_heads, int head_dim, float scale, int window, int num_splits,
-                                         int sink, const void* gate, int ldg, cudaStream_t stream) {
+// sigmoid(gate[b, h*head_dim + i]) before it is stored.  softcap > 0: a score s (scale included) becomes
+// softcap * tanh(s / softcap).  keep_first > 0 (with a window): positions [0, keep_first) stay visible.
+extern "C" int rl_attention_decode_masked(const void* q, int ldq, const void* k_pool, const void* v_pool,
+                                          const int* page_table, int max_pages, const int* seq_slots, const int* kv_lens,
+                                          void* out, int ldo, float* scratch, const int* plan, int num_seqs, int num_heads,
+                                          int num_kv_heads, int head_dim, float scale, int window, int num_splits,
+                                          int sink, const void* gate, int ldg, float softcap, int keep_first,
+                                          cudaStream_t stream) {
   RL_REQUIRE(gate == nullptr || ldg >= num_heads * head_dim, "rl_attention_decode: the gate's row stride is too small");
-  const DecFinish fin = {sink, (const __nv_bfloat16*)gate, ldg};
+  RL_REQUIRE(softcap >= 0.f && keep_first >= 0, "rl_attention_decode: negative soft cap or number of kept first tokens");
+  const DecFinish fin = {sink, (const __nv_bfloat16*)gate, ldg, softcap, window > 0 ? keep_first : 0};
   RL_REQUIRE(rl_attention_decode_supported(num_heads, num_kv_heads, head_dim),
              "rl_attention_decode: unsupported shape (heads %d, KV heads %d, head_dim %d): needs head_dim 64 or 128 "
              "and at most 16 heads per KV head", num_heads, num_kv_heads, head_dim);
@@ -684,6 +704,16 @@ extern "C" int rl_attention_decode_gated(const void* q, int ldq, const void* k_p
                              part_ml, plan, num_seqs, num_heads, num_kv_heads, scale, window, num_splits, fin, stream);
   return launch_decode<128>(q, ldq, k_pool, v_pool, page_table, max_pages, seq_slots, kv_lens, out, ldo, part_o,
                             part_ml, plan, num_seqs, num_heads, num_kv_heads, scale, window, num_splits, fin, stream);
+}
+
+extern "C" int rl_attention_decode_gated(const void* q, int ldq, const void* k_pool, const void* v_pool,
+                                         const int* page_table, int max_pages, const int* seq_slots, const int* kv_lens,
+                                         void* out, int ldo, float* scratch, const int* plan, int num_seqs, int num_heads,
+                                         int num_kv_heads, int head_dim, float scale, int window, int num_splits,
+                                         int sink, const void* gate, int ldg, cudaStream_t stream) {
+  return rl_attention_decode_masked(q, ldq, k_pool, v_pool, page_table, max_pages, seq_slots, kv_lens, out, ldo, scratch, plan,
+                                    num_seqs, num_heads, num_kv_heads, head_dim, scale, window, num_splits, sink, gate, ldg, 0.f, 0,
+                                    stream);
 }
 
 extern "C" int rl_attention_decode(const void* q, int ldq, const void* k_pool, const void* v_pool,

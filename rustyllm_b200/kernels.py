@@ -91,6 +91,9 @@ _SIGNATURES = {
     "rl_attention_decode_gated": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
                                   _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
                                   _c_int, _c_void_p, _c_int, _c_void_p],
+    "rl_attention_decode_masked": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                                   _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int,
+                                   _c_int, _c_void_p, _c_int, _c_float, _c_int, _c_void_p],
     "rl_attention_prefill_gated": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p,
                                    _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int,
                                    _c_int, _c_void_p, _c_int, _c_void_p],
@@ -1018,14 +1021,16 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
                      num_kv_heads: int, head_dim: int, scale: float, window: int = 0,
                      num_splits: Optional[int] = None, scratch: Optional[torch.Tensor] = None,
                      plan: Optional[torch.Tensor] = None, cluster: bool = False, sink: bool = False,
-                     gate: Optional[torch.Tensor] = None) -> None:
+                     gate: Optional[torch.Tensor] = None, softcap: float = 0.0, keep_first: int = 0) -> None:
     """One token per sequence over the bf16 cache, split over the context (tensor cores).
     q: [B, >= H*hd] bf16 (a view into the qkv buffer is fine); out: [B, H*hd] bf16.
     ``num_splits``: chunks per sequence; with a ``plan`` (from ``decode_plan`` with the
     same sequences, window and splits) that many on average, dealt to the sequences by
     length; with one split a ``plan`` from ``decode_order`` starts the longest sequences first.
     ``cluster`` (2, 4 or 8 splits, no plan): the chunks of a sequence run as a
-    thread-block cluster and combine through shared memory - no scratch, one kernel."""
+    thread-block cluster and combine through shared memory - no scratch, one kernel.
+    ``softcap`` > 0: a score s (scale included) becomes softcap * tanh(s / softcap); ``keep_first``: with a
+    window, positions [0, keep_first) stay visible."""
     _need(q, "q", torch.bfloat16, contiguous=False); _need(k_pool, "k_pool", torch.bfloat16)
     _need(v_pool, "v_pool", torch.bfloat16); _need(out, "out", torch.bfloat16)
     _need(page_table, "page_table", torch.int32); _need(seq_slots, "seq_slots", torch.int32)
@@ -1047,11 +1052,11 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
         assert plan.numel() >= 4 * B * num_splits + 2 * B
     ldq = q.stride(0) if B > 1 else max(q.stride(0), num_heads * head_dim)
     gptr, ldg = _gate_args(gate, B, num_heads * head_dim, 2)
-    _check(library().rl_attention_decode_gated(
+    _check(library().rl_attention_decode_masked(
         q.data_ptr(), ldq, k_pool.data_ptr(), v_pool.data_ptr(), page_table.data_ptr(), page_table.shape[1],
         seq_slots.data_ptr(), kv_lens.data_ptr(), out.data_ptr(), out.stride(0), _ptr(scratch), _ptr(plan), B,
         num_heads, num_kv_heads, head_dim, float(scale), int(window), int(num_splits), int(bool(sink)), gptr, ldg,
-        _stream()), "rl_attention_decode")
+        float(softcap or 0.0), int(keep_first or 0), _stream()), "rl_attention_decode")
     _count(2 if num_splits > 1 and not cluster else 1)
 
 
@@ -1149,8 +1154,10 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
     key heads (``value_dim``) run on the any-shape kernel; the tensor-core kernels take
     one width for both.  ``sink``: one more term of score 0 in the softmax's denominator.
     ``gate`` [M, H*vd]: the output is multiplied by sigmoid(gate)."""
-    if (value_dim is not None and value_dim != head_dim) or softcap or (keep_first and window):
-        # soft-capped scores and kept first tokens exist in the any-shape kernel only
+    masked = bool(softcap or (keep_first and window))
+    if (value_dim is not None and value_dim != head_dim) or (masked and not (
+            step.is_decode and attention_decode_supported(q.dtype, num_heads, num_kv_heads, head_dim))):
+        # soft-capped scores and kept first tokens: the any-shape kernel and the decode kernel have them
         attention_simt(q, k_pool, v_pool, page_table, step.slot_of_token, step.positions, out,
                        num_heads, num_kv_heads, head_dim, scale, window, value_dim=value_dim, sink=sink, gate=gate,
                        softcap=softcap, keep_first=keep_first)
@@ -1170,7 +1177,7 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
                     order = derived[("decode_order", int(window))] = decode_order(step.seq_slots, step.kv_lens, window)
             attention_decode(q, k_pool, v_pool, page_table, step.seq_slots, step.kv_lens, out,
                              num_heads, num_kv_heads, head_dim, scale, window, num_splits=cluster, plan=order,
-                             cluster=cluster > 1, sink=sink, gate=gate)
+                             cluster=cluster > 1, sink=sink, gate=gate, softcap=softcap, keep_first=keep_first)
             return
         plan = None
         derived = getattr(step, "derived", None)     # what layers of one step share
@@ -1180,7 +1187,8 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
             if plan is None:
                 plan = derived[key] = decode_plan(step.seq_slots, step.kv_lens, window, splits)
         attention_decode(q, k_pool, v_pool, page_table, step.seq_slots, step.kv_lens, out,
-                         num_heads, num_kv_heads, head_dim, scale, window, num_splits=splits, plan=plan, sink=sink, gate=gate)
+                         num_heads, num_kv_heads, head_dim, scale, window, num_splits=splits, plan=plan, sink=sink, gate=gate,
+                         softcap=softcap, keep_first=keep_first)
         return
     if not step.is_decode and attention_prefill_tc_supported(q.dtype, num_heads, num_kv_heads, head_dim) \
             and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 \

@@ -135,7 +135,8 @@ class GQAttention(Mixer):
         k_pool, v_pool = group.k_pool(layer), group.v_pool(layer)
         pos = self.position
         x = xn.weighted if isinstance(xn, NormedInput) else xn
-        prepared = self.conv_taps or self.qk_norm or pos.magnitude != 1.0
+        magnitude = getattr(pos, "magnitude", 1.0)      # a position kind of its own need not know the attribute
+        prepared = self.conv_taps or self.qk_norm or magnitude != 1.0
         q = qkv
         if prepared:
             # convolution, head norms, rotation and the cache write in one kernel behind the product
@@ -145,7 +146,7 @@ class GQAttention(Mixer):
                 raise K.KernelError("interleaved rotary pairs behind a convolution or head norms are not built")
             K.qkv_prepare(qkv, q, self.conv_w if self.conv_taps else None, cache.state if self.conv_taps > 1 else None,
                           self.q_norm_w, self.k_norm_w, self.qk_norm_eps, step.positions, step.slot_of_token, group.page_table,
-                          pos.inv_freq, pos.rotary_dim, pos.magnitude, H, G, hd, vd,
+                          pos.inv_freq, pos.rotary_dim, magnitude, H, G, hd, vd,
                           k_pool if cache.writes else None, v_pool if cache.writes else None)
             if self.conv_taps > 1 and cache.writes:
                 K.short_conv_state(qkv, self.conv_taps, step.cu_seqlens, step.seq_slots, cache.state)

@@ -7,7 +7,7 @@ itself and states every mechanism from its definition (t: time, h: the sublayer'
   norm           n(y) = y / sqrt(mean(y^2) + eps) * w
   layer          x += n1(mixer(x));  x += n2(ff(x));  x += n_s(P_s (gelu_tanh(G_s x) * e_token[layer]))
   short conv     y_t = sum_j w[:, j] u_{t - taps + 1 + j}   (u = 0 before the sequence starts)
-  attention      q, k, v = conv(W h + b); per head q, k <- n(q), n(k); partial rotary with YaRN
+  attention      q, k, v = conv(W h + b); per head q, k <- n(q), n(k); partial rotary with stretched
                  frequencies; s_ij = cap * tanh((q_i . k_j) * scale / cap) for j <= i and
                  (i - j < window or j < keep_first); softmax; Wo
   state space    [z | x | B | C | dt] = W h; (x, B, C) <- silu(conv + bias); dt <- softplus(dt + dt_bias);
@@ -130,6 +130,16 @@ def visible(i: int, j: int, window: Optional[int], keep_first: int) -> bool:
     return j <= i and (window is None or i - j < window or j < keep_first)
 
 
+def attend(q_i: torch.Tensor, keys: torch.Tensor, values: torch.Tensor, i: int, window: Optional[int], keep_first: int,
+           scale: float, cap: Optional[float]) -> torch.Tensor:
+    """One query at position i over the keys [T, dim] and values [T, vdim] of its key/value head."""
+    js = [j for j in range(i + 1) if visible(i, j, window, keep_first)]
+    s = (keys[js] @ q_i) * scale
+    if cap:
+        s = cap * torch.tanh(s / cap)
+    return torch.softmax(s, dim=0) @ values[js]
+
+
 def windowed_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: dict, eps: float) -> torch.Tensor:
     T = h.shape[0]
     H, G, hd, vd = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
@@ -147,18 +157,13 @@ def windowed_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: d
         q = rotate(q, range(T), rot["dims"], freqs, mult)
         k = rotate(k, range(T), rot["dims"], freqs, mult)
     mask = m.get("mask") or {}
-    window, keep = mask.get("size"), mask.get("keep_first", 0)
+    window, keep = mask.get("size"), mask.get("keep_first") or 0
     cap = m.get("softcap")
     out = torch.zeros(T, H, vd, dtype=F64)
     for a in range(H):
         g = a // (H // G)
         for i in range(T):
-            js = [j for j in range(i + 1) if visible(i, j, window, keep)]
-            s = torch.stack([(q[i, a] * k[j, g]).sum() for j in js]) * m["scale"]
-            if cap:
-                s = cap * torch.tanh(s / cap)
-            pr = torch.softmax(s, dim=0)
-            out[i, a] = (pr[:, None] * torch.stack([v[j, g] for j in js])).sum(0)
+            out[i, a] = attend(q[i, a], k[:, g], v[:, g], i, window, keep, m["scale"], cap)
     return out.reshape(T, H * vd) @ w[p + "o"].T
 
 

@@ -1,0 +1,529 @@
+"""The Mogutar design on the GPU against the plain implementation (tests/plain_mogutar.py): each mechanism alone
+at its kernel's own interface, then the engine - the residual stream after every layer, whole prompts, prompts
+against token-by-token decoding, portions down to two tokens, unequal batches against each request alone, slots and
+pages used again, the edges of windows and of the kept first tokens in prompts and in decoding, long decoding - and
+greedy generation through ``Runner.generate``."""
+import functools
+import math
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import mogutar_configs as C
+import plain_mogutar as P
+from gpu_helpers import BF16_REL_MAX, BF16_REL_MEAN, F32_REL, random_tokens
+
+pytestmark = pytest.mark.gpu
+DTYPES = ["float32", "bfloat16"]
+NAMES = list(C.CONFIGS)
+DEV = "cuda:0"
+F64 = torch.float64
+
+
+@pytest.fixture(scope="module")
+def dirs(tmp_path_factory):
+    root = tmp_path_factory.mktemp("mogutar")
+    made = {(n, "float32"): C.write_model(n, str(root / n)) for n in NAMES}
+    # the bfloat16 runs: routers whose choices do not hinge on rounding (see mogutar_configs)
+    made.update({(n, "bfloat16"): C.write_model(n, str(root / (n + "_calm")), calm_router=True) for n in NAMES})
+    return made
+
+
+@functools.lru_cache(maxsize=None)
+def _plain(d):
+    return P.load_model_dir(d)
+
+
+_LOGITS = {}
+
+
+def plain_logits(d, tokens):
+    key = (d, tuple(tokens))
+    if key not in _LOGITS:
+        cfg, w = _plain(d)
+        _LOGITS[key] = P.forward(cfg, w, list(tokens))
+    return _LOGITS[key]
+
+
+@functools.lru_cache(maxsize=None)
+def runner(d, dtype, max_cache_tokens=64 * 40, max_batch=8):
+    from rustyllm_b200 import Runner
+    return Runner.from_path(d, dtype=dtype, max_cache_tokens=max_cache_tokens, max_batch=max_batch)[0]
+
+
+def close(got, ref, dtype, cfg, what):
+    """32-bit: 3e-5 of a logit row's rms.  bfloat16: the bounds of gpu_helpers (derived for three pre-norm layers,
+    whose sublayers add a small term to the stream) times three and grown with the square root of the layers: here
+    every layer adds three terms that are normed to unit size, noise included, so a term's own rounding noise
+    (about 1 % with sharp attention) is the stream's (the bfloat16 runs use routers without close calls)."""
+    got, ref = got.detach().to("cpu", F64), ref.detach().to("cpu", F64)
+    assert got.shape == ref.shape, f"{what}: {tuple(got.shape)} vs {tuple(ref.shape)}"
+    assert torch.isfinite(got).all(), f"{what}: non-finite logits"
+    err = (got - ref).abs() / ref.pow(2).mean(dim=-1, keepdim=True).sqrt().clamp_min(1e-30)
+    if dtype == "float32":
+        assert err.max().item() <= F32_REL, f"{what}: {err.max().item():.3e} (row {err.max(dim=-1).values.argmax().item()})"
+    else:
+        grow = 3.0 * math.sqrt(max(1.0, len(cfg["layers"]) / 3.0))
+        rows = err.max(dim=-1).values
+        # the rows' errors have a long tail: where two large scores of a sharp attention row are nearly equal, the
+        # rounding of q and k moves its weights by several per cent.  Up to 2 % of the rows (at least one) may exceed the bound, none
+        # three times the bound (a lost key, a key too many or another expert show as 0.5 and more)
+        over = (rows > BF16_REL_MAX * grow).double().sum().item()
+        assert over <= max(1.0, 0.02 * rows.numel()), f"{what}: {over:.0f} of {rows.numel()} rows above {BF16_REL_MAX * grow:.3f} (worst {rows.max().item():.3e})"
+        assert rows.max().item() <= 3.0 * BF16_REL_MAX * grow, f"{what}: max {rows.max().item():.3e} (row {rows.argmax().item()})"
+        assert err.mean().item() <= BF16_REL_MEAN * grow, f"{what}: mean {err.mean().item():.3e}"
+
+
+def i32(x):
+    return torch.tensor(x, dtype=torch.int32, device=DEV)
+
+
+def tdt(dtype):
+    return torch.float32 if dtype == "float32" else torch.bfloat16
+
+
+def rounded(x, dtype):
+    """What the kernel is given: the float64 test data rounded to the run's storage type."""
+    return x.to(tdt(dtype)).to(F64)
+
+
+def tol(dtype):
+    return dict(rtol=2e-5, atol=2e-5) if dtype == "float32" else dict(rtol=1.2e-2, atol=1.2e-2)
+
+
+def state_area(slots, nbytes, pad=256):
+    """A per-slot state as the cache hands it out: a column range of a wider area, zeroed."""
+    area = torch.zeros((slots, pad + nbytes + pad), dtype=torch.uint8, device=DEV)
+    return area, area[:, pad:pad + nbytes]
+
+
+# =========================================================================== mechanisms alone
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("taps,portions", [(4, [(5, 1, 1, 2, 30), (1, 1, 1, 1, 7)]), (2, [(3, 9), (12,)]), (1, [(4, 4), (8,)]),
+                                           (8, [(2, 2, 2, 20), (26,)])])
+def test_short_convolution_across_steps(dtype, taps, portions):
+    """Two sequences packed in every step, cut differently, against the whole-sequence convolution; the state
+    carries the last taps - 1 inputs, also through portions shorter than the filter."""
+    from rustyllm_b200 import kernels as K
+    torch.manual_seed(taps)
+    Cn = 37
+    n = [sum(p) for p in portions]
+    assert len(set(len(p) for p in portions)) <= 2
+    u = [rounded(torch.randn(t, Cn, dtype=F64), dtype) for t in n]
+    w, b = torch.randn(Cn, taps, dtype=F64).float().double(), torch.randn(Cn, dtype=F64).float().double()
+    ref = [P.silu(P.short_conv(x, w, b)) for x in u]
+    area, state = state_area(4, 4 * (taps - 1) * Cn)
+    slots = [3, 1]
+    at = [0, 0]
+    got = [[], []]
+    for step in range(max(len(p) for p in portions)):
+        live = [s for s in range(2) if step < len(portions[s])]
+        cnt = [portions[s][step] for s in live]
+        rows = torch.cat([u[s][at[s]:at[s] + c] for s, c in zip(live, cnt)])
+        wide = torch.zeros((rows.shape[0], Cn + 11), dtype=tdt(dtype), device=DEV)       # a view with a wider row stride
+        wide[:, 5:5 + Cn] = rows.to(tdt(dtype)).to(DEV)
+        uin = wide[:, 5:5 + Cn]
+        out = torch.empty((rows.shape[0], Cn), dtype=tdt(dtype), device=DEV)
+        slot_of_token = i32([slots[s] for s, c in zip(live, cnt) for _ in range(c)])
+        cu = i32([0] + list(np.cumsum(cnt)))
+        K.short_conv(uin, w.float().to(DEV), b.float().to(DEV), True, slot_of_token, state, out)
+        K.short_conv_state(uin, taps, cu, i32([slots[s] for s in live]), state)
+        o = 0
+        for s, c in zip(live, cnt):
+            got[s].append(out[o:o + c].double().cpu())
+            o += c
+            at[s] += c
+    for s in range(2):
+        torch.testing.assert_close(torch.cat(got[s]), ref[s], **tol(dtype))
+    assert int(area[:, :256].any()) == 0 and int(area[:, -256:].any()) == 0       # nothing written outside the state
+
+
+def _scan_reference(q, k, v, a, b, skip, hpg):
+    T, H, dv = v.shape
+    out = torch.zeros(T, H, dv, dtype=F64)
+    for h in range(H):
+        S = torch.zeros(q.shape[2], dv, dtype=F64)
+        for t in range(T):
+            S = a[t, h] * S + b[t, h] * torch.outer(k[t, h // hpg], v[t, h])
+            out[t, h] = S.T @ q[t, h // hpg] + skip[h] * v[t, h]
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,hpg,dk,dv", [(3, 1, 24, 12), (4, 2, 16, 8), (2, 2, 40, 20), (1, 1, 72, 48), (2, 1, 130, 5)])
+@pytest.mark.parametrize("mode", ["decay", "selective"])
+def test_linear_recurrence_across_steps(dtype, H, hpg, dk, dv, mode):
+    """S_t = a_t S_{t-1} + b_t k_t v_t^T, o_t = S_t^T q_t (+ skip v_t), two sequences, cut into portions of 1 to
+    dozens of tokens, against the loop over time; the state is carried in the per-slot area."""
+    from rustyllm_b200 import kernels as K
+    torch.manual_seed(H * 100 + dk)
+    portions = [(21, 1, 1, 2, 17), (1, 40)]
+    n = [sum(p) for p in portions]
+    G = H // hpg
+    area, state = state_area(3, 4 * H * dk * dv)
+    rate = torch.tensor([0.5, 0.9, 0.99, 0.999][:H], dtype=F64) if mode == "decay" else (-1.0 + torch.randn(H, dtype=F64)).float().double()
+    dt_bias = torch.randn(H, dtype=F64).float().double()
+    skip = torch.randn(H, dtype=F64).float().double()
+    data, ref = [], []
+    for t in n:
+        q, k = rounded(torch.randn(t, G, dk, dtype=F64), dtype), rounded(torch.randn(t, G, dk, dtype=F64) / math.sqrt(dk), dtype)
+        v, dt = rounded(torch.randn(t, H, dv, dtype=F64), dtype), rounded(torch.randn(t, H, dtype=F64), dtype)
+        data.append((q, k, v, dt))
+        if mode == "decay":
+            qa, ka, va = P.silu(q), P.silu(k), P.silu(v)
+            ref.append(_scan_reference(qa, ka, va, rate.expand(t, H), torch.ones(t, H, dtype=F64), torch.zeros(H, dtype=F64), hpg))
+        else:
+            step_size = P.softplus(dt + dt_bias)
+            ref.append(_scan_reference(q, k, v, torch.exp(-torch.exp(rate) * step_size), step_size, skip, hpg))
+    slots, at, got = [2, 0], [0, 0], [[], []]
+    for step in range(max(len(p) for p in portions)):
+        live = [s for s in range(2) if step < len(portions[s])]
+        cnt = [portions[s][step] for s in live]
+        cat = lambda j, width: torch.cat([data[s][j][at[s]:at[s] + c].reshape(c, width) for s, c in zip(live, cnt)]).to(tdt(dtype)).to(DEV)
+        q, k, v, dt = cat(0, G * dk), cat(1, G * dk), cat(2, H * dv), cat(3, H)
+        out = torch.empty((sum(cnt), H * dv), dtype=torch.float32, device=DEV)
+        cu, ss = i32([0] + list(np.cumsum(cnt))), i32([slots[s] for s in live])
+        if mode == "decay":
+            K.linear_scan(q, k, v, out, state, cu, ss, H, hpg, dk, dv, rate.float().to(DEV), silu=True)
+        else:
+            K.linear_scan(q, k, v, out, state, cu, ss, H, hpg, dk, dv, rate.float().to(DEV), dt_raw=dt, dt_bias=dt_bias.float().to(DEV),
+                          skip=skip.float().to(DEV))
+        o = 0
+        for s, c in zip(live, cnt):
+            got[s].append(out[o:o + c].double().cpu().view(c, H, dv))
+            o += c
+            at[s] += c
+    for s in range(2):
+        # everything behind the loads is 32-bit in both runs: the bound is float32's
+        torch.testing.assert_close(torch.cat(got[s]), ref[s], rtol=1e-4, atol=1e-4)
+    assert int(area[:, :256].any()) == 0 and int(area[:, -256:].any()) == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_norms_on_a_sublayers_output(dtype):
+    from rustyllm_b200 import kernels as K
+    torch.manual_seed(5)
+    M, d, eps = 7, 52, 1e-5
+    x, y0, y1 = (torch.randn(M, d, dtype=F64).float() for _ in range(3))
+    w = (1 + 0.1 * torch.randn(d, dtype=F64)).float()
+    for terms in (1, 2):
+        xd = x.clone().to(DEV)
+        xb = torch.empty((M, d), dtype=torch.bfloat16, device=DEV)
+        K.norm_add(xd, y0.to(DEV), 1.2, y1.to(DEV) if terms == 2 else None, 0.9, w.to(DEV), eps, xb)
+        s = 1.2 * y0.double() + (0.9 * y1.double() if terms == 2 else 0.0)
+        ref = x.double() + P.rms_norm(s, w.double(), eps)
+        torch.testing.assert_close(xd.double().cpu(), ref, rtol=1e-5, atol=1e-5)
+        assert torch.equal(xb, xd.to(torch.bfloat16))
+    # gate first, norm in groups; norm first, gate last
+    n, groups = 48, 3
+    y = torch.randn(M, n, dtype=F64).float()
+    gate = rounded(torch.randn(M, n, dtype=F64), dtype)
+    wn = (1 + 0.1 * torch.randn(n, dtype=F64)).float()
+    out = torch.empty((M, n), dtype=tdt(dtype), device=DEV)
+    K.gated_norm(y.to(DEV), gate.to(tdt(dtype)).to(DEV), wn.to(DEV), eps, out, groups=groups, gate_act="silu", gate_first=True)
+    ref = P.rms_norm((y.double() * P.silu(gate)).view(M, groups, n // groups), None, eps).reshape(M, n) * wn.double()
+    torch.testing.assert_close(out.double().cpu(), ref, **tol(dtype))
+    K.gated_norm(y.to(DEV), gate.to(tdt(dtype)).to(DEV), wn.to(DEV), eps, out, groups=1, gate_act="sigmoid", gate_first=False)
+    ref = P.rms_norm(y.double(), wn.double(), eps) * P.sigmoid(gate)
+    torch.testing.assert_close(out.double().cpu(), ref, **tol(dtype))
+    # the token's learned vector times gelu of a projection
+    V, cols, col0, width = 11, 30, 12, 6
+    t = rounded(torch.randn(M, width, dtype=F64), dtype)
+    table = rounded(torch.randn(V, cols, dtype=F64), dtype)
+    tokens = [3, 0, 10, 10, 7, 1, 2]
+    g = torch.empty((M, width), dtype=tdt(dtype), device=DEV)
+    K.gelu_gate(t.to(tdt(dtype)).to(DEV), i32(tokens), table.to(tdt(dtype)).to(DEV), col0, g)
+    torch.testing.assert_close(g.double().cpu(), P.gelu_tanh(t) * table[tokens][:, col0:col0 + width], **tol(dtype))
+
+
+@pytest.mark.parametrize("E,top,groups", [(12, 2, (3, 2)), (12, 3, (4, 1)), (6, 6, None), (9, 1, (9, 3)), (40, 3, (5, 2)), (7, 2, (1, 1))])
+@pytest.mark.parametrize("M", [5, 200])
+def test_router_with_sigmoid_scores_and_groups(E, top, groups, M):
+    """Both forms of the router (one kernel a token; a matrix product and a selection) against the plain choice,
+    with corrections large enough to change it and negative choice scores."""
+    from rustyllm_b200 import kernels as K
+    torch.manual_seed(E + top)
+    d = 24
+    x = torch.randn(M, d, dtype=F64).float()
+    wr = (1.5 * torch.randn(E, d, dtype=F64) / math.sqrt(d)).float()
+    corr = (torch.randn(E, dtype=F64) - 0.8).float()
+    ids = torch.empty((M, top), dtype=torch.int32, device=DEV)
+    wts = torch.empty((M, top), dtype=torch.float32, device=DEV)
+    count, keep = groups or (1, 1)
+    gdict = None if groups is None else {"count": count, "keep": keep}
+    for form in ("one kernel", "product"):
+        if form == "one kernel":
+            K.moe_route_sigmoid(x.to(DEV), wr.to(DEV), corr.to(DEV), top, count, keep, ids, wts)
+        else:
+            logits = (x.double() @ wr.double().T).float().to(DEV)
+            K.moe_select_sigmoid(logits, corr.to(DEV), top, count, keep, ids, wts)
+        for m in range(M):
+            want_ids, want_w = P.route(x[m].double(), wr.double(), corr.double(), top, gdict)
+            assert ids[m].tolist() == want_ids, f"{form}, token {m}"
+            torch.testing.assert_close(wts[m].double().cpu(), torch.stack(want_w), rtol=1e-5, atol=1e-6)
+
+
+def _masked_attention(dtype, H, G, hd, vd, window, keep_first, scale, cap, q, k, v, portions):
+    """q, k, v of one sequence through the cache and the attention dispatcher in ``portions``."""
+    from rustyllm_b200 import kernels as K
+    from rustyllm_b200.cache.sequence_cache import KVNeed, SequenceCache
+    from rustyllm_b200.engine.step import StepState
+    n = q.shape[0]
+    cache = SequenceCache([KVNeed(G, hd, window, vd, keep_first)], [None], 64 * (n // 64 + 3), tdt(dtype), DEV, max_slots=3)
+    cache.alloc_slot()
+    slot = cache.alloc_slot()
+    group, layer = cache.kv_entry(0)
+    inv_freq = torch.zeros(1, dtype=torch.float32, device=DEV)
+    outs, at = [], 0
+    for cnt in portions:
+        cache.prepare([slot], [cnt])
+        st = StepState(cnt, 1, i32([0] * cnt), i32(list(range(at, at + cnt))), i32([slot] * cnt), i32([0, cnt]), i32([slot]),
+                       i32([at + cnt]), i32([]), [cnt], [at + cnt], cnt, at + cnt, cnt == 1)
+        qkv = torch.cat([q[at:at + cnt], k[at:at + cnt], v[at:at + cnt]], dim=1).to(tdt(dtype)).to(DEV).contiguous()
+        qo = torch.empty((cnt, H * hd), dtype=tdt(dtype), device=DEV)
+        K.qkv_prepare(qkv, qo, None, None, None, None, 0.0, st.positions, st.slot_of_token, group.page_table, inv_freq, 0, 1.0,
+                      H, G, hd, vd, group.k_pool(layer), group.v_pool(layer))
+        out = torch.empty((cnt, H * vd), dtype=tdt(dtype), device=DEV)
+        K.attention(qo, group.k_pool(layer), group.v_pool(layer), group.page_table, st, out, H, G, hd, scale, window or 0,
+                    value_dim=vd, softcap=cap or 0.0, keep_first=keep_first)
+        cache.commit([slot], [cnt])
+        cache.check()
+        outs.append(out.double().cpu())
+        at += cnt
+    K.check_device_errors()
+    return torch.cat(outs)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("H,G,hd,vd", [(4, 2, 16, 24), (2, 1, 64, 64), (2, 2, 128, 128)])
+@pytest.mark.parametrize("window,keep_first", [(9, 2), (70, 5), (64, 64), (130, 3), (1, 1), (None, 0), (40, 0)])
+def test_one_key_stands_out_at_the_edges_of_window_and_kept_tokens(dtype, H, G, hd, vd, window, keep_first):
+    """Scores are flat but for one key that a query meets with a score 12 above the rest: its value must dominate
+    the output exactly while the key is inside the window or among the kept first tokens, and vanish the token
+    after - in a prompt's portion, at a portion's start and in single tokens - with pages given back on the way."""
+    torch.manual_seed(hd + (window or 0))
+    n = 230
+    scale, cap = 1.0 / math.sqrt(hd), 40.0
+    special = [keep_first - 1, keep_first, 100] if keep_first else [0, 100]
+    q = 0.05 * torch.randn(n, H * hd, dtype=F64)
+    k = 0.05 * torch.randn(n, G * hd, dtype=F64)
+    v = torch.randn(n, G * vd, dtype=F64)
+    probe = torch.zeros(hd, dtype=F64)
+    probe[3] = 1.0
+    for j in special:                         # these keys point along the probe direction, every query looks there;
+        kept = j < keep_first                 # a kept key stands out by 7.5 in score, the others by 12
+        k[j].view(G, hd)[:] += (2.5 if kept else 4.0) * hd ** 0.25 * probe
+    q.view(n, H, hd)[:] += 3.0 * hd ** 0.25 * probe
+    q, k, v = rounded(q, dtype), rounded(k, dtype), rounded(v, dtype)
+    ref = torch.zeros(n, H, vd, dtype=F64)
+    for a in range(H):
+        g = a // (H // G)
+        for i in range(n):
+            ref[i, a] = P.attend(q[i].view(H, hd)[a], k.view(n, G, hd)[:, g], v.view(n, G, vd)[:, g], i, window, keep_first, scale, cap)
+    # the construction does what it should: the far key is seen with weight > 0.9 inside and < 0.1 outside
+    far = 100
+    if window is not None and window < 100:
+        seen_at = far + window - 1
+        for i, inside in ((seen_at, True), (seen_at + 1, False)):
+            d_far = (ref[i, 0] - v.view(n, G, vd)[far, 0]).norm() / v.view(n, G, vd)[far, 0].norm()
+            assert (d_far < 0.35) == inside, (i, float(d_far))
+    for portions in ([n], [97, 2, 1, 1, 64, 65], [1] * 12 + [88, 130], [150] + [1] * 80):
+        got = _masked_attention(dtype, H, G, hd, vd, window, keep_first, scale, cap, q, k, v, portions).view(n, H, vd)
+        torch.testing.assert_close(got, ref, **(dict(rtol=1e-4, atol=1e-4) if dtype == "float32" else dict(rtol=2e-2, atol=2e-2)))
+
+
+# =========================================================================== the engine
+@pytest.mark.parametrize("name", NAMES)
+def test_residual_stream_after_every_layer(dirs, name):
+    d = dirs[name, "float32"]
+    cfg, w = _plain(d)
+    toks = random_tokens(cfg["vocab"], 45, 11)
+    ref_layers = []
+    P.forward(cfg, w, toks, ref_layers)
+    r = runner(d, "float32")
+    rec = []
+    saved = [b.forward for b in r.model.blocks]
+    try:
+        for b in r.model.blocks:
+            def f(x, step, cache, _o=b.forward, **kw):
+                out = _o(x, step, cache, **kw)
+                rec.append(x.clone())
+                return out
+            b.forward = f
+        s = r.engine.alloc_slot()
+        r.engine.step([s], [toks], None)
+        r.engine.free_slot(s)
+    finally:
+        for b, f in zip(r.model.blocks, saved):
+            b.forward = f
+    assert len(rec) == len(ref_layers)
+    for i, (got, ref) in enumerate(zip(rec, ref_layers)):
+        scale = ref.pow(2).mean().sqrt()
+        assert ((got.double().cpu() - ref).abs().max() / scale).item() < 2e-5, f"layer {i}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_whole_prompts_and_first_tokens(dirs, name, dtype):
+    d = dirs[name, dtype]
+    cfg, _ = _plain(d)
+    r = runner(d, dtype)
+    for n, seed in ((1, 1), (2, 2), (5, 3), (150, 4)):
+        toks = random_tokens(cfg["vocab"], n, seed)
+        s = r.engine.alloc_slot()
+        got = r.engine.step([s], [toks], "all")
+        r.engine.free_slot(s)
+        close(got, plain_logits(d, toks), dtype, cfg, f"{name} whole {n}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_prompt_then_token_by_token_equals_whole(dirs, name, dtype):
+    """Most of a request in one step, its last 90 tokens one by one (the windows, the kept tokens and a page border
+    pass over decoded tokens), and 140 single tokens from the very first."""
+    d = dirs[name, dtype]
+    cfg, _ = _plain(d)
+    r = runner(d, dtype)
+    for n, cut, seed in ((215, 125, 21), (140, 1, 22)):
+        toks = random_tokens(cfg["vocab"], n, seed)
+        ref = plain_logits(d, toks)
+        s = r.engine.alloc_slot()
+        rows = [r.engine.step([s], [toks[:cut]], "all")]
+        for t in range(cut, n):
+            rows.append(r.engine.step([s], [[toks[t]]], "last"))
+        r.engine.free_slot(s)
+        close(torch.cat(rows), ref, dtype, cfg, f"{name} decode from {cut}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+@pytest.mark.parametrize("size", [2, 3, 7, 64, 100])
+def test_prompt_in_portions(dirs, name, dtype, size):
+    d = dirs[name, dtype]
+    cfg, _ = _plain(d)
+    r = runner(d, dtype)
+    toks = random_tokens(cfg["vocab"], 203, 31 + size)
+    s = r.engine.alloc_slot()
+    rows = [r.engine.step([s], [toks[at:at + size]], "all") for at in range(0, len(toks), size)]
+    r.engine.free_slot(s)
+    got = torch.cat(rows)
+    close(got, plain_logits(d, toks), dtype, cfg, f"{name} portions of {size}")
+    if dtype == "float32":
+        # the same kernels sum in the same order whatever the cut (but for the router's logits, which a step of 128
+        # tokens or more computes as a matrix product): whole and cut agree to a few roundings
+        s = r.engine.alloc_slot()
+        whole = r.engine.step([s], [toks], "all")
+        r.engine.free_slot(s)
+        assert ((whole - got).abs().max() / whole.abs().max()).item() < 1e-5
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_unequal_batches_reuse_slots_and_pages(dirs, name, dtype):
+    """Two batches of unequal requests through a cache that only just holds one of them: prompts together, then
+    decoded together while the short ones leave; the second batch takes the slots, pages and state of the first."""
+    from rustyllm_b200 import Runner
+    d = dirs[name, dtype]
+    cfg, _ = _plain(d)
+    r = Runner.from_path(d, dtype=dtype, max_cache_tokens=64 * 9, max_batch=4)[0]
+    eng = r.engine
+    for batch, lens in enumerate(([1, 130, 66, 200], [190, 3, 64, 120])):
+        reqs = [random_tokens(cfg["vocab"], n, 40 + 10 * batch + i) for i, n in enumerate(lens)]
+        tail = 20
+        slots = [eng.alloc_slot() for _ in reqs]
+        heads = [max(1, len(t) - tail) for t in reqs]
+        got = [[] for _ in reqs]
+        out = eng.step(slots, [t[:h] for t, h in zip(reqs, heads)], "all")
+        o = 0
+        for i, h in enumerate(heads):
+            got[i].append(out[o:o + h])
+            o += h
+        at = list(heads)
+        live = [i for i in range(len(reqs)) if at[i] < len(reqs[i])]
+        for i in range(len(reqs)):
+            if i not in live:
+                eng.free_slot(slots[i])
+        while live:
+            out = eng.step([slots[i] for i in live], [[reqs[i][at[i]]] for i in live], "last")
+            for j, i in enumerate(live):
+                got[i].append(out[j:j + 1])
+                at[i] += 1
+            for i in [i for i in live if at[i] == len(reqs[i])]:
+                eng.free_slot(slots[i])
+            live = [i for i in live if at[i] < len(reqs[i])]
+        r.cache.check()
+        for i, t in enumerate(reqs):
+            close(torch.cat(got[i]), plain_logits(d, t), dtype, cfg, f"{name} batch {batch} request {i}")
+    assert r.cache.slots.held_count == 0 and all(g.pages.held_count == 0 for g in r.cache.groups)
+
+
+@pytest.mark.parametrize("seed", range(10))
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_configurations_drawn_at_random(tmp_path, seed, dtype):
+    cfg = C.random_config(seed)
+    d = C.write_model("random", str(tmp_path / "m"), seed=seed, cfg=cfg, calm_router=dtype == "bfloat16")
+    from rustyllm_b200 import Runner
+    r = Runner.from_path(d, dtype=dtype, max_cache_tokens=64 * 12, max_batch=4)[0]
+    a, b = random_tokens(cfg["vocab"], 150, seed), random_tokens(cfg["vocab"], 77, seed + 100)
+    sa, sb = r.engine.alloc_slot(), r.engine.alloc_slot()
+    out = r.engine.step([sa, sb], [a[:100], b[:70]], "all")
+    rows_a, rows_b = [out[:100]], [out[100:]]
+    out = r.engine.step([sb, sa], [b[70:], a[100:130]], "all")
+    rows_b.append(out[:7]); rows_a.append(out[7:])
+    r.engine.free_slot(sb)
+    for t in range(130, 150):
+        rows_a.append(r.engine.step([sa], [[a[t]]], "last"))
+    r.engine.free_slot(sa)
+    close(torch.cat(rows_a), plain_logits(d, a), dtype, cfg, f"random {seed} a")
+    close(torch.cat(rows_b), plain_logits(d, b), dtype, cfg, f"random {seed} b")
+
+
+# =========================================================================== generation and entry points
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_greedy_generation_through_the_runner(dirs, name, dtype):
+    from rustyllm_b200 import GenerationOptions, SamplerConfig
+    d = dirs[name, dtype]
+    cfg, w = _plain(d)
+    r = runner(d, dtype)
+    prompts = [random_tokens(cfg["vocab"], n, 60 + n) for n in (3, 70, 20)]
+    new = 24
+    results = r.generate(prompts, GenerationOptions(max_tokens=new, sampler=SamplerConfig.greedy(), ignore_eos=True))
+    for p, got in zip(prompts, results):
+        tokens = list(got.token_ids)
+        assert len(tokens) == new
+        # follow the framework's own tokens and require that each is the plain implementation's best, or within
+        # rounding of it (bfloat16 may pick the other of two near-equal logits)
+        ref = plain_logits(d, p + tokens[:-1])[len(p) - 1:]
+        for i, t in enumerate(tokens):
+            best = ref[i].max().item()
+            slack = 1e-3 if dtype == "float32" else 0.15 * ref[i].std().item()
+            assert ref[i, t].item() >= best - slack, f"{name} request of {len(p)}, new token {i}"
+
+
+def test_trace_replay_and_command_line(dirs, tmp_path):
+    import json
+    toks = random_tokens(C.CONFIGS["T"]["vocab"], 90, 77)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": toks[:80], "want": [0, 79]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": toks[80:81], "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": toks[81:], "want": [8]}], "end": ["a"]}]
+    for dtype in DTYPES:
+        d = dirs["T", dtype]
+        cfg, _ = _plain(d)
+        out = tmp_path / dtype
+        p = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", d, "--dtype", dtype, "--out", str(out), "--max-tokens", "128"],
+                           input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=600)
+        assert p.returncode == 0, p.stderr[-2000:]
+        assert [l for l in p.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+        assert not (out / "1.f32").exists()
+        ref = plain_logits(d, toks)
+        got0 = torch.from_numpy(np.fromfile(out / "0.f32", dtype="<f4").reshape(2, -1))
+        got2 = torch.from_numpy(np.fromfile(out / "2.f32", dtype="<f4").reshape(1, -1))
+        close(torch.cat([got0, got2]), ref[[0, 79, 89]], dtype, cfg, f"trace {dtype}")
+    p = subprocess.run([sys.executable, os.path.join(root, "bin", "rustyllm"), d, "--inspect"], capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0 and "Mogutar" in p.stdout, p.stderr[-2000:]
