@@ -195,7 +195,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                             const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slots,
                             const int* __restrict__ kv_lens, int num_seqs, __nv_bfloat16* __restrict__ out, int ldo,
                             int H, int G, float scale_log2e, int window, int* __restrict__ err,
-                            const int* __restrict__ tile_order, int sink, const __nv_bfloat16* __restrict__ gate, int ldg) {
+                            const int* __restrict__ tile_order, int sink, const __nv_bfloat16* __restrict__ gate, int ldg,
+                            float cap_in, float cap_out, int keep_first) {
   extern __shared__ uint8_t fa_smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)fa_smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* q_tile = smem;                                   // [2 halves][128 x 64]
@@ -274,7 +275,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int b = *s_seq;
   const bool have_work = b < num_seqs;      // the grid is sized exactly; defensive
   const int h = blockIdx.x, gkv = h / (H / G);
-  int row0 = 0, q_len = 0, kv_len = 0, qt0 = 0, rows_here = 0, kt_begin = 0, kt_end = 0, start_pos = 0;
+  int row0 = 0, q_len = 0, kv_len = 0, qt0 = 0, rows_here = 0, kt_begin = 0, kt_end = 0, start_pos = 0, kept_tiles = 0;
   const int* pages = page_table;
   if (have_work) {
     row0 = cu_seqlens[b]; q_len = cu_seqlens[b + 1] - row0; kv_len = kv_lens[b];
@@ -285,8 +286,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int last_pos = start_pos + qt0 + rows_here - 1;
     const int first_key = window > 0 ? max(0, start_pos + qt0 + 1 - window) : 0;
     kt_begin = first_key / TK; kt_end = last_pos / TK + 1;
+    // kept first tokens: the key tiles that hold positions [0, keep_first) and lie wholly in front of the
+    // window's first tile are walked first (place i of the walk is tile i there, kt_begin + i - kept_tiles behind)
+    kept_tiles = window > 0 ? min((keep_first + TK - 1) / TK, kt_begin) : 0;
   }
-  const int num_kt = kt_end - kt_begin;
+  const int num_kt = kt_end - kt_begin + kept_tiles;
+  auto tile_of = [&](int i) { return i < kept_tiles ? i : kt_begin + (i - kept_tiles); };
 
   if (warp < 4) {
     // ---- the feeding warps: a few registers are enough; the rest goes to the softmax warps ----
@@ -301,7 +306,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // keys and values have rings of their own: the keys' stage is free once the S of its tile
         // is done, the values' once its P V is; whichever is free first is filled first
         auto load = [&](int i, bool values) {
-          const int kt = kt_begin + i, st = i % (values ? V_STAGES : K_STAGES);
+          const int kt = tile_of(i), st = i % (values ? V_STAGES : K_STAGES);
           const int p0 = pages[2 * kt];
           const int p1 = (2 * kt + 1) * RL_PAGE < kv_len ? pages[2 * kt + 1] : p0;   // beyond the sequence: any valid page (all masked)
           const int r0 = (p0 * G + gkv) * RL_PAGE, r1 = (p1 * G + gkv) * RL_PAGE;
@@ -399,7 +404,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       bool ok = true;                                         // warp-uniform
       const float2 sc2 = make_float2(scale_log2e, scale_log2e);
       for (int i = grp; i < num_kt && ok; i += 2) {
-        const int sb = grp, key0 = (kt_begin + i) * TK;       // S buffer = tile parity = group
+        const int sb = grp, key0 = tile_of(i) * TK;           // S buffer = tile parity = group
         ok = __all_sync(0xffffffffu, fa_wait(fa_smem_u32(&s_full[sb]), (i >> 1) & 1, abort_flag));
         if (!ok) break;
         fa_fence_after();
@@ -413,6 +418,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         fa_fence_before();
         __syncwarp();
         if (lane == 0) fa_arrive(fa_smem_u32(&s_free[sb]));
+        if (cap_in > 0.f) {
+          // soft cap: a score s (scale included) becomes cap * tanh(s / cap); kept in units of the raw product
+          // (cap_in = scale / cap, cap_out = cap / scale) so that what follows stays as it is.
+          // tanh(x) = 1 - 2 / (e^{2x} + 1): two fast special-function operations, absolute error about 1e-7
+#pragma unroll
+          for (int j = 0; j < TK; ++j) {
+            const float e2x = fa_exp2(__uint_as_float(sa[j]) * cap_in * 2.8853900817779268f);
+            sa[j] = __float_as_uint(cap_out * (1.0f - __fdividef(2.0f, e2x + 1.0f)));
+          }
+        }
         // The tile on the diagonal (no window) has code of its own, by 32-key chunks; every other tile
         // runs straight-line code over all 128 scores, which the scheduler can reorder freely.
         const bool diag = window <= 0 && key0 + TK - 1 > start_pos + qt0;     // warp-uniform
@@ -423,7 +438,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
             for (int j = 0; j < TK; ++j) {
               const int key = key0 + j;
-              if (!(key <= pos && key > pos - window)) sa[j] = 0xff800000u;          // -inf
+              if (!(key <= pos && (key > pos - window || key < keep_first))) sa[j] = 0xff800000u;          // -inf
             }
           }
 #pragma unroll
@@ -638,12 +653,17 @@ extern "C" int rl_attention_prefill_tc_supported(int num_heads, int num_kv_heads
 // everywhere (see the note at the top of this file).
 // sink != 0: one more term of score 0 in the softmax's denominator.  gate (may be null): bf16 [M, ldg],
 // 16-byte aligned with ldg a multiple of 8; the output is multiplied by sigmoid(gate[m, h*head_dim + i]).
-extern "C" int rl_attention_prefill_tc_gated(const void* q, int ldq, const void* k_pool, const void* v_pool, int num_pages,
-                                             const int* page_table, int max_pages, const int* cu_seqlens,
-                                             const int* seq_slots, const int* kv_lens, int num_seqs, int num_tiles,
-                                             int num_tokens, void* out, int ldo, int num_heads, int num_kv_heads, int head_dim,
-                                             float scale, int window, int* err, const int* tile_order, int sink,
-                                             const void* gate, int ldg, cudaStream_t stream) {
+// softcap > 0: a score s (scale included) becomes softcap * tanh(s / softcap).  keep_first > 0 (with a window):
+// positions [0, keep_first) stay visible behind the window.
+extern "C" int rl_attention_prefill_tc_masked(const void* q, int ldq, const void* k_pool, const void* v_pool, int num_pages,
+                                              const int* page_table, int max_pages, const int* cu_seqlens,
+                                              const int* seq_slots, const int* kv_lens, int num_seqs, int num_tiles,
+                                              int num_tokens, void* out, int ldo, int num_heads, int num_kv_heads, int head_dim,
+                                              float scale, int window, int* err, const int* tile_order, int sink,
+                                              const void* gate, int ldg, float softcap, int keep_first, cudaStream_t stream) {
+  RL_REQUIRE(softcap >= 0.f && keep_first >= 0 && scale > 0.f, "rl_attention_prefill_tc: negative soft cap or number of kept first tokens, or a scale that is not positive");
+  const float cap_in = softcap > 0.f ? scale / softcap : 0.f, cap_out = softcap > 0.f ? softcap / scale : 0.f;
+  if (window <= 0) keep_first = 0;
   RL_REQUIRE(gate == nullptr || (ldg >= num_heads * head_dim && ldg % 8 == 0 && ((uintptr_t)gate & 15) == 0),
              "rl_attention_prefill_tc: the gate must be 16-byte aligned with a row stride that is a multiple of 8 and holds all heads");
   RL_REQUIRE(rl_attention_prefill_tc_supported(num_heads, num_kv_heads, head_dim),
@@ -676,16 +696,27 @@ extern "C" int rl_attention_prefill_tc_gated(const void* q, int ldq, const void*
       ? rl_launch_pdl(attention_prefill_tc_kernel<128>, dim3(num_heads, num_tiles), dim3(FA_THREADS), (size_t)FaSizes<128>::SMEM, stream,
                       mq, mk, mv, page_table, max_pages, cu_seqlens, seq_slots, kv_lens, num_seqs,
                       (__nv_bfloat16*)out, ldo, num_heads, num_kv_heads, scale * 1.4426950408889634f, window, err, tile_order,
-                      sink, (const __nv_bfloat16*)gate, ldg)
+                      sink, (const __nv_bfloat16*)gate, ldg, cap_in, cap_out, keep_first)
       : rl_launch_pdl(attention_prefill_tc_kernel<64>, dim3(num_heads, num_tiles), dim3(FA_THREADS), (size_t)FaSizes<64>::SMEM, stream,
                       mq, mk, mv, page_table, max_pages, cu_seqlens, seq_slots, kv_lens, num_seqs,
                       (__nv_bfloat16*)out, ldo, num_heads, num_kv_heads, scale * 1.4426950408889634f, window, err, tile_order,
-                      sink, (const __nv_bfloat16*)gate, ldg);
+                      sink, (const __nv_bfloat16*)gate, ldg, cap_in, cap_out, keep_first);
   if (e != cudaSuccess) {
     rl_set_error("rl_attention_prefill_tc: launch failed: %s", cudaGetErrorString(e));
     return RL_ERR_CUDA;
   }
   return RL_OK;
+}
+
+extern "C" int rl_attention_prefill_tc_gated(const void* q, int ldq, const void* k_pool, const void* v_pool, int num_pages,
+                                             const int* page_table, int max_pages, const int* cu_seqlens,
+                                             const int* seq_slots, const int* kv_lens, int num_seqs, int num_tiles,
+                                             int num_tokens, void* out, int ldo, int num_heads, int num_kv_heads, int head_dim,
+                                             float scale, int window, int* err, const int* tile_order, int sink,
+                                             const void* gate, int ldg, cudaStream_t stream) {
+  return rl_attention_prefill_tc_masked(q, ldq, k_pool, v_pool, num_pages, page_table, max_pages, cu_seqlens, seq_slots, kv_lens,
+                                        num_seqs, num_tiles, num_tokens, out, ldo, num_heads, num_kv_heads, head_dim, scale, window,
+                                        err, tile_order, sink, gate, ldg, 0.f, 0, stream);
 }
 
 extern "C" int rl_attention_prefill_tc(const void* q, int ldq, const void* k_pool, const void* v_pool, int num_pages,

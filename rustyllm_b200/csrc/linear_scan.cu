@@ -9,98 +9,175 @@
 // Query and key heads may be shared by `hpg` consecutive heads (head h reads group h / hpg).  With act = 1
 // q, k and v pass through silu as they are loaded.  Everything behind the loads is 32-bit.
 //
-// A block owns SCAN_COLS columns of one head's state of one sequence and walks the sequence's tokens of
-// the step in order; SCAN_R neighbouring lanes share a column (lane r holds rows r, r + SCAN_R, ...) and
-// add their parts of q . S[:, col] by shuffles.  Tokens are staged SCAN_TILE at a time in shared memory.
+// A block owns 8 or 16 columns of one head's state of one sequence and walks the sequence's tokens of
+// the step in order; R neighbouring lanes share a column (each holds NPT consecutive rows) and add their
+// parts of q . S[:, col] by shuffles.  Tokens are staged SCAN_TILE at a time in shared memory.  The walk is
+// one dependent multiply-add a state element and token; everything else (the loads of q and k from shared
+// memory, the dot product, the shuffles) is latency to hide, so R grows with dk (8, 16, 32: a block of 128,
+// 256 or 512 threads, at most 8 state elements a thread): more warps an SM, fewer instructions a thread.
 // The order of every sum is fixed by the sizes alone, so a position's output does not depend on how the
 // sequence was cut into steps or on the batch.  State layout per slot: [H, dv, dk].
 #include <math.h>
 
 #include "common.cuh"
 
-#define SCAN_R 8
-#define SCAN_COLS 16
 #define SCAN_TILE 16
 #define SCAN_MAX_DK 256
 
-__device__ __forceinline__ float scan_silu(float z) { return z / (1.0f + expf(-z)); }
+// silu at the load: accurate in a 32-bit run; with the fast exponential and division in a bfloat16 run, whose
+// projections carry 8 bits
+__device__ __forceinline__ float scan_silu(float z, float) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float scan_silu(float z, __nv_bfloat16) { return __fdividef(z, 1.0f + __expf(-z)); }
 
-template <typename T, int NPT>
-__global__ void __launch_bounds__(SCAN_R * SCAN_COLS)
+template <typename T, int NPT, int R, int SCAN_COLS>
+__global__ void __launch_bounds__(R * SCAN_COLS)
 linear_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, int ldk, const T* __restrict__ v, int ldv,
                    const T* __restrict__ dt_raw, int lddt, const float* __restrict__ dt_bias, const float* __restrict__ rate,
                    const float* __restrict__ skip, int mode, int act, const int* __restrict__ cu_seqlens,
                    const int* __restrict__ seq_slots, float* __restrict__ state, long long state_stride,
                    float* __restrict__ out, int ldo, int H, int hpg, int dk, int dv) {
-  __shared__ float s_q[SCAN_TILE][NPT * SCAN_R], s_k[SCAN_TILE][NPT * SCAN_R];
-  __shared__ float s_v[SCAN_TILE][SCAN_COLS], s_a[SCAN_TILE], s_b[SCAN_TILE];
+  constexpr int DKP = NPT * R;                  // dk rounded up to what the lanes of a column hold: a power of two
+  constexpr int THREADS = R * SCAN_COLS;
+  // Two shapes.  Many tokens a sequence (NPT <= 8): a lane holds NPT consecutive rows (16-byte loads from shared
+  // memory in the walk) and the next tile's q, k, v and step sizes are fetched into registers while this
+  // tile is walked, so that no load from global memory is waited for.  Few tokens (NPT > 8, 8 lanes a column): a
+  // lane holds rows r, r + 8, ... (the state's loads and stores are whole lines), staged directly.
+  constexpr bool LONG = NPT <= 8;
+  static_assert(!LONG || (R * SCAN_COLS >= SCAN_TILE * SCAN_COLS && NPT % 4 == 0), "the long shape stages a tile's values one a thread");
+  // rows beyond dk are staged as zeros, so the walk needs no bounds: their state stays zero
+  __shared__ __align__(16) float s_q[SCAN_TILE][DKP], s_k[SCAN_TILE][DKP];
+  __shared__ float s_v[SCAN_TILE][SCAN_COLS], s_bv[SCAN_TILE][SCAN_COLS], s_a[SCAN_TILE];
   rl_pdl_trigger();
   rl_pdl_wait();
   const int b = blockIdx.x, h = blockIdx.y;
-  const int tid = threadIdx.x, r = tid % SCAN_R, c = tid / SCAN_R;
+  const int tid = threadIdx.x, r = tid % R, c = tid / R;
   const int col = blockIdx.z * SCAN_COLS + c;
   const bool live = col < dv;
   const int lo = cu_seqlens[b], hi = cu_seqlens[b + 1];
+  auto row_of = [&](int i) { return LONG ? NPT * r + i : r + R * i; };
   float* st = state + (size_t)seq_slots[b] * state_stride + ((size_t)h * dv + (live ? col : 0)) * dk;
   float S[NPT];
 #pragma unroll
-  for (int i = 0; i < NPT; ++i) {
-    const int n = r + SCAN_R * i;
-    S[i] = (live && n < dk) ? st[n] : 0.f;
-  }
+  for (int i = 0; i < NPT; ++i) S[i] = (live && row_of(i) < dk) ? st[row_of(i)] : 0.f;
   const int qk0 = (h / hpg) * dk;
   const float skip_h = skip ? skip[h] : 0.f;
-  for (int t0 = lo; t0 < hi; t0 += SCAN_TILE) {
-    const int nt = min(SCAN_TILE, hi - t0);
-    __syncthreads();
-    for (int idx = tid; idx < nt * dk; idx += SCAN_R * SCAN_COLS) {
-      const int tt = idx / dk, n = idx % dk;
-      float qv = rl_ld(q + (size_t)(t0 + tt) * ldq + qk0 + n), kv = rl_ld(k + (size_t)(t0 + tt) * ldk + qk0 + n);
-      if (act) { qv = scan_silu(qv); kv = scan_silu(kv); }
+  const float rate_h = rate[h], bias_h = mode ? dt_bias[h] : 0.f;
+  const float neg_rate = mode ? -expf(rate_h) : 0.f;
+
+  // what a thread stages of a tile: NPT elements of q and of k (element idx = tid + j * THREADS of the tile's
+  // [SCAN_TILE, DKP]), one of v (threads below SCAN_TILE * SCAN_COLS) with its token's raw step size
+  constexpr int VT = SCAN_TILE * SCAN_COLS;
+  float fq[LONG ? NPT : 1], fk[LONG ? NPT : 1], fv = 0.f, fdt = 0.f;
+  auto fetch = [&](int t0, int nt) {            // raw values of the tile at t0 into registers (zeros outside)
+#pragma unroll
+    for (int j = 0; j < (LONG ? NPT : 1); ++j) {
+      const int idx = tid + j * THREADS, tt = idx / DKP, n = idx % DKP;
+      const bool in = tt < nt && n < dk;
+      fq[j] = in ? rl_ld(q + (size_t)(t0 + tt) * ldq + qk0 + n) : 0.f;
+      fk[j] = in ? rl_ld(k + (size_t)(t0 + tt) * ldk + qk0 + n) : 0.f;
+    }
+    if (THREADS >= VT ? tid < VT : true) {
+      const int tt = tid / SCAN_COLS, cc = blockIdx.z * SCAN_COLS + tid % SCAN_COLS;
+      fv = (tt < nt && cc < dv) ? rl_ld(v + (size_t)(t0 + tt) * ldv + (size_t)h * dv + cc) : 0.f;
+      fdt = (mode && tt < nt) ? rl_ld(dt_raw + (size_t)(t0 + tt) * lddt + h) : 0.f;
+    }
+  };
+  auto step_size = [&](float raw) { const float z = raw + bias_h; return z > 20.0f ? z : log1pf(expf(z)); };
+  auto commit = [&]() {                         // the fetched values, activated, into shared memory
+#pragma unroll
+    for (int j = 0; j < (LONG ? NPT : 1); ++j) {
+      const int idx = tid + j * THREADS, tt = idx / DKP, n = idx % DKP;
+      float qv = fq[j], kv = fk[j];
+      if (act && n < dk) { qv = scan_silu(qv, T()); kv = scan_silu(kv, T()); }
       s_q[tt][n] = qv;
       s_k[tt][n] = kv;
     }
-    for (int idx = tid; idx < nt * SCAN_COLS; idx += SCAN_R * SCAN_COLS) {
-      const int tt = idx / SCAN_COLS, cc = blockIdx.z * SCAN_COLS + idx % SCAN_COLS;
-      float vv = cc < dv ? rl_ld(v + (size_t)(t0 + tt) * ldv + (size_t)h * dv + cc) : 0.f;
-      if (act) vv = scan_silu(vv);
-      s_v[tt][idx % SCAN_COLS] = vv;
+    if (tid < VT) {
+      const int tt = tid / SCAN_COLS;
+      const float vv = act ? scan_silu(fv, T()) : fv;
+      const float dt = mode ? step_size(fdt) : 1.0f;
+      s_v[tt][tid % SCAN_COLS] = vv;
+      s_bv[tt][tid % SCAN_COLS] = dt * vv;
+      if (tid % SCAN_COLS == 0) s_a[tt] = mode ? expf(neg_rate * dt) : rate_h;
     }
-    if (tid < nt) {
-      if (mode == 0) {
-        s_a[tid] = rate[h];
-        s_b[tid] = 1.0f;
-      } else {
-        const float z = rl_ld(dt_raw + (size_t)(t0 + tid) * lddt + h) + dt_bias[h];
-        const float dt = z > 20.0f ? z : log1pf(expf(z));
-        s_a[tid] = expf(-expf(rate[h]) * dt);
-        s_b[tid] = dt;
+  };
+  if (LONG && lo < hi) fetch(lo, min(SCAN_TILE, hi - lo));
+  for (int t0 = lo; t0 < hi; t0 += SCAN_TILE) {
+    const int nt = min(SCAN_TILE, hi - t0);
+    __syncthreads();
+    if (LONG) {
+      commit();
+    } else {
+      // few tokens: straight from global memory (THREADS < VT here, so loops)
+      for (int idx = tid; idx < nt * DKP; idx += THREADS) {
+        const int tt = idx / DKP, n = idx % DKP;
+        float qv = 0.f, kv = 0.f;
+        if (n < dk) {
+          qv = rl_ld(q + (size_t)(t0 + tt) * ldq + qk0 + n);
+          kv = rl_ld(k + (size_t)(t0 + tt) * ldk + qk0 + n);
+          if (act) { qv = scan_silu(qv, T()); kv = scan_silu(kv, T()); }
+        }
+        s_q[tt][n] = qv;
+        s_k[tt][n] = kv;
+      }
+      for (int idx = tid; idx < nt * SCAN_COLS; idx += THREADS) {
+        const int tt = idx / SCAN_COLS, cc = blockIdx.z * SCAN_COLS + idx % SCAN_COLS;
+        float vv = cc < dv ? rl_ld(v + (size_t)(t0 + tt) * ldv + (size_t)h * dv + cc) : 0.f;
+        if (act) vv = scan_silu(vv, T());
+        const float dt = mode ? step_size(rl_ld(dt_raw + (size_t)(t0 + tt) * lddt + h)) : 1.0f;
+        s_v[tt][idx % SCAN_COLS] = vv;
+        s_bv[tt][idx % SCAN_COLS] = dt * vv;
+        if (idx % SCAN_COLS == 0) s_a[tt] = mode ? expf(neg_rate * dt) : rate_h;
       }
     }
     __syncthreads();
-    for (int tt = 0; tt < nt; ++tt) {
-      const float a = s_a[tt], vv = s_v[tt][c], bv = s_b[tt] * vv;
-      float part = 0.f;
+    if (LONG && t0 + SCAN_TILE < hi) fetch(t0 + SCAN_TILE, min(SCAN_TILE, hi - t0 - SCAN_TILE));   // in flight during the walk
+    // the walk itself: loads from shared memory and multiply-adds only; every token's part of q . S[:, col]
+    // stays in a register, and the lanes' parts are added afterwards, sixteen independent chains of shuffles
+    float part[SCAN_TILE];
 #pragma unroll
-      for (int i = 0; i < NPT; ++i) {
-        const int n = r + SCAN_R * i;
-        if (n < dk) {
-          S[i] = fmaf(a, S[i], bv * s_k[tt][n]);
-          part = fmaf(S[i], s_q[tt][n], part);
+    for (int tt = 0; tt < SCAN_TILE; ++tt) {
+      part[tt] = 0.f;
+      if (tt < nt) {
+        const float a = s_a[tt], bv = s_bv[tt][c];
+        if (LONG) {
+          const float4* k4 = reinterpret_cast<const float4*>(&s_k[tt][NPT * r]);
+          const float4* q4 = reinterpret_cast<const float4*>(&s_q[tt][NPT * r]);
+#pragma unroll
+          for (int i = 0; i < NPT / 4; ++i) {
+            const float4 kk = k4[i], qq = q4[i];
+            S[4 * i] = fmaf(a, S[4 * i], bv * kk.x);
+            S[4 * i + 1] = fmaf(a, S[4 * i + 1], bv * kk.y);
+            S[4 * i + 2] = fmaf(a, S[4 * i + 2], bv * kk.z);
+            S[4 * i + 3] = fmaf(a, S[4 * i + 3], bv * kk.w);
+            part[tt] = fmaf(S[4 * i], qq.x, part[tt]);
+            part[tt] = fmaf(S[4 * i + 1], qq.y, part[tt]);
+            part[tt] = fmaf(S[4 * i + 2], qq.z, part[tt]);
+            part[tt] = fmaf(S[4 * i + 3], qq.w, part[tt]);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < NPT; ++i) {
+            S[i] = fmaf(a, S[i], bv * s_k[tt][r + R * i]);
+            part[tt] = fmaf(S[i], s_q[tt][r + R * i], part[tt]);
+          }
         }
       }
-      part += __shfl_xor_sync(0xffffffffu, part, 1);
-      part += __shfl_xor_sync(0xffffffffu, part, 2);
-      part += __shfl_xor_sync(0xffffffffu, part, 4);
-      if (r == 0 && live) out[(size_t)(t0 + tt) * ldo + (size_t)h * dv + col] = part + skip_h * vv;
+    }
+#pragma unroll
+    for (int tt = 0; tt < SCAN_TILE; ++tt) {
+      if (tt < nt) {
+        float p = part[tt];
+#pragma unroll
+        for (int o = 1; o < R; o <<= 1) p += __shfl_xor_sync(0xffffffffu, p, o);
+        if (r == 0 && live) out[(size_t)(t0 + tt) * ldo + (size_t)h * dv + col] = p + skip_h * s_v[tt][c];
+      }
     }
   }
   if (live) {
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) {
-      const int n = r + SCAN_R * i;
-      if (n < dk) st[n] = S[i];
-    }
+    for (int i = 0; i < NPT; ++i)
+      if (row_of(i) < dk) st[row_of(i)] = S[i];
   }
 }
 
@@ -108,16 +185,20 @@ template <typename T>
 static int scan_launch(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, const void* dt_raw, int lddt,
                        const float* dt_bias, const float* rate, const float* skip, int mode, int act, const int* cu_seqlens,
                        const int* seq_slots, int num_seqs, float* state, long long state_stride, float* out, int ldo, int H,
-                       int hpg, int dk, int dv, cudaStream_t stream) {
-  const dim3 grid(num_seqs, H, (dv + SCAN_COLS - 1) / SCAN_COLS);
-  const int threads = SCAN_R * SCAN_COLS;
-#define SCAN_GO(NPT)                                                                                                        \
-  rl_launch_pdl(linear_scan_kernel<T, NPT>, grid, threads, 0, stream, (const T*)q, ldq, (const T*)k, ldk, (const T*)v, ldv, \
-                (const T*)dt_raw, lddt, dt_bias, rate, skip, mode, act, cu_seqlens, seq_slots, state, state_stride, out, ldo, H, hpg, dk, dv)
-  if (dk <= 4 * SCAN_R) SCAN_GO(4);
-  else if (dk <= 8 * SCAN_R) SCAN_GO(8);
-  else if (dk <= 16 * SCAN_R) SCAN_GO(16);
-  else SCAN_GO(32);
+                       int hpg, int dk, int dv, int wide, cudaStream_t stream) {
+#define SCAN_GO(NPT, R, COLS)                                                                                                      \
+  rl_launch_pdl(linear_scan_kernel<T, NPT, R, COLS>, dim3(num_seqs, H, (dv + COLS - 1) / COLS), R * COLS, 0, stream, (const T*)q, ldq, \
+                (const T*)k, ldk, (const T*)v, ldv, (const T*)dt_raw, lddt, dt_bias, rate, skip, mode, act, cu_seqlens, seq_slots,      \
+                state, state_stride, out, ldo, H, hpg, dk, dv)
+  // columns of the state a block: 16 in single-token steps (fewer, larger blocks: 0.52 against 0.43 of the copy
+  // bandwidth at 64 sequences), 8 in long steps (two blocks an SM whose phases overlap: 575 against 655 us for
+  // 2,048 tokens of 16 heads of 128 x 128)
+  if (!wide) {                      // few tokens a sequence: the state's traffic is the work; 8 lanes a column
+    if (dk <= 128) SCAN_GO(16, 8, 16);
+    else SCAN_GO(32, 8, 16);
+  } else if (dk <= 64) SCAN_GO(4, 16, 8);
+  else if (dk <= 128) SCAN_GO(4, 32, 8);
+  else SCAN_GO(8, 32, 8);
 #undef SCAN_GO
   return 0;
 }
@@ -125,11 +206,13 @@ static int scan_launch(const void* q, int ldq, const void* k, int ldk, const voi
 // q, k: [M, ld] with group g at columns [g * dk, (g + 1) * dk); v: [M, ldv] with head h at [h * dv, (h + 1) * dv);
 // dt_raw [M, lddt] (mode 1; same dtype); dt_bias, rate, skip: float [H] (skip may be null; rate is the decay itself
 // in mode 0 and the logarithm of the decay rate in mode 1).  state: float, this recurrence's [H, dv, dk] of slot s
-// at state + s * state_stride.  out: float [M, ldo].
+// at state + s * state_stride.  out: float [M, ldo].  wide != 0: the launch shape for many tokens a sequence (more
+// lanes a column of the state); 0: for few (single-token steps).  The two differ in the order of a dot product's sum.
 extern "C" int rl_linear_scan(const void* q, int ldq, const void* k, int ldk, const void* v, int ldv, const void* dt_raw,
                               int lddt, int dtype, const float* dt_bias, const float* rate, const float* skip, int mode, int act,
                               const int* cu_seqlens, const int* seq_slots, int num_seqs, float* state, long long state_stride,
-                              float* out, int ldo, int num_heads, int heads_per_group, int dk, int dv, cudaStream_t stream) {
+                              float* out, int ldo, int num_heads, int heads_per_group, int dk, int dv, int wide,
+                              cudaStream_t stream) {
   RL_REQUIRE(num_seqs >= 0 && num_heads > 0 && heads_per_group > 0 && num_heads % heads_per_group == 0, "rl_linear_scan: bad sizes");
   RL_REQUIRE(dk > 0 && dk <= SCAN_MAX_DK && dv > 0, "rl_linear_scan: dk %d outside (0, %d] or dv %d", dk, SCAN_MAX_DK, dv);
   RL_REQUIRE(mode == 0 || (mode == 1 && dt_raw != nullptr && dt_bias != nullptr), "rl_linear_scan: mode %d, or no step sizes", mode);
@@ -138,10 +221,10 @@ extern "C" int rl_linear_scan(const void* q, int ldq, const void* k, int ldk, co
   if (num_seqs == 0) return RL_OK;
   if (dtype == RL_F32)
     scan_launch<float>(q, ldq, k, ldk, v, ldv, dt_raw, lddt, dt_bias, rate, skip, mode, act, cu_seqlens, seq_slots, num_seqs, state,
-                       state_stride, out, ldo, num_heads, heads_per_group, dk, dv, stream);
+                       state_stride, out, ldo, num_heads, heads_per_group, dk, dv, wide, stream);
   else if (dtype == RL_BF16)
     scan_launch<__nv_bfloat16>(q, ldq, k, ldk, v, ldv, dt_raw, lddt, dt_bias, rate, skip, mode, act, cu_seqlens, seq_slots, num_seqs,
-                               state, state_stride, out, ldo, num_heads, heads_per_group, dk, dv, stream);
+                               state, state_stride, out, ldo, num_heads, heads_per_group, dk, dv, wide, stream);
   else
     RL_REQUIRE(false, "rl_linear_scan: unknown dtype %d", dtype);
   RL_LAUNCH_CHECK("rl_linear_scan");

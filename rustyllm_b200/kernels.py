@@ -58,7 +58,7 @@ _SIGNATURES = {
                        _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
     "rl_linear_scan": [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p,
                        _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_ll, _c_void_p, _c_int, _c_int,
-                       _c_int, _c_int, _c_int, _c_void_p],
+                       _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "rl_norm_add": [_c_void_p, _c_void_p, _c_float, _c_void_p, _c_float, _c_void_p, _c_float, _c_int, _c_int, _c_void_p, _c_void_p],
     "rl_gated_norm": [_c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_float, _c_int, _c_int, _c_int,
                       _c_void_p, _c_int, _c_void_p],
@@ -100,6 +100,9 @@ _SIGNATURES = {
     "rl_attention_prefill_tc_gated": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
                                       _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float,
                                       _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p],
+    "rl_attention_prefill_tc_masked": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p,
+                                       _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_float,
+                                       _c_int, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_float, _c_int, _c_void_p],
     "rl_attention_decode_plan": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "rl_attention_decode_order": [_c_void_p, _c_void_p, _c_int, _c_int, _c_void_p, _c_void_p],
     "rl_attention_decode_places": [_c_int],
@@ -593,7 +596,7 @@ def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Te
     _check(library().rl_linear_scan(q.data_ptr(), q.stride(0), k.data_ptr(), k.stride(0), v.data_ptr(), v.stride(0), _ptr(dt_raw), lddt,
                                     _dt(q), _ptr(dt_bias), rate.data_ptr(), _ptr(skip), mode, int(bool(silu)), cu_seqlens.data_ptr(),
                                     seq_slots.data_ptr(), seq_slots.numel(), sp, ss, out.data_ptr(), out.stride(0), num_heads,
-                                    heads_per_group, dk, dv, _stream()), "rl_linear_scan")
+                                    heads_per_group, dk, dv, int(M >= 4 * seq_slots.numel()), _stream()), "rl_linear_scan")
     _count()
 
 
@@ -1118,7 +1121,7 @@ def attention_prefill_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
                          cu_seqlens: torch.Tensor, seq_slots: torch.Tensor, kv_lens: torch.Tensor, q_lens,
                          out: torch.Tensor, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                          window: int = 0, tile_order: Optional[torch.Tensor] = None, sink: bool = False,
-                         gate: Optional[torch.Tensor] = None) -> None:
+                         gate: Optional[torch.Tensor] = None, softcap: float = 0.0, keep_first: int = 0) -> None:
     """The same as ``attention_prefill`` on tcgen05 tensor cores (head size 64 or 128).  The cache
     pools must hold finite values everywhere (the cache zero-fills them when it allocates them).
     ``tile_order``: what ``prefill_tile_order`` made for this step (the blocks then start heaviest first)."""
@@ -1135,11 +1138,12 @@ def attention_prefill_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Te
         assert tile_order.numel() == 2 * tiles
     ldq = q.stride(0) if q.shape[0] > 1 else max(q.stride(0), num_heads * head_dim)
     gptr, ldg = _gate_args(gate, q.shape[0], num_heads * head_dim, 16)
-    _check(library().rl_attention_prefill_tc_gated(
+    _check(library().rl_attention_prefill_tc_masked(
         q.data_ptr(), ldq, k_pool.data_ptr(), v_pool.data_ptr(), k_pool.shape[0], page_table.data_ptr(),
         page_table.shape[1], cu_seqlens.data_ptr(), seq_slots.data_ptr(), kv_lens.data_ptr(), B, tiles, q.shape[0],
         out.data_ptr(), out.stride(0), num_heads, num_kv_heads, head_dim, float(scale), int(window),
-        _tc_error_word(q.device).data_ptr(), _ptr(tile_order), int(bool(sink)), gptr, ldg, _stream()), "rl_attention_prefill_tc")
+        _tc_error_word(q.device).data_ptr(), _ptr(tile_order), int(bool(sink)), gptr, ldg, float(softcap or 0.0),
+        int(keep_first or 0), _stream()), "rl_attention_prefill_tc")
     _count()
 
 
@@ -1155,9 +1159,13 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
     one width for both.  ``sink``: one more term of score 0 in the softmax's denominator.
     ``gate`` [M, H*vd]: the output is multiplied by sigmoid(gate)."""
     masked = bool(softcap or (keep_first and window))
-    if (value_dim is not None and value_dim != head_dim) or (masked and not (
+    tc_prefill = (not step.is_decode and attention_prefill_tc_supported(q.dtype, num_heads, num_kv_heads, head_dim)
+                  and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0
+                  and (gate is None or (gate.data_ptr() % 16 == 0 and gate.stride(0) % 8 == 0)))
+    if (value_dim is not None and value_dim != head_dim) or (masked and not tc_prefill and not (
             step.is_decode and attention_decode_supported(q.dtype, num_heads, num_kv_heads, head_dim))):
-        # soft-capped scores and kept first tokens: the any-shape kernel and the decode kernel have them
+        # soft-capped scores and kept first tokens: the any-shape kernel, the decode kernel and the tcgen05 prompt
+        # kernel have them (the mma.sync prompt kernel does not)
         attention_simt(q, k_pool, v_pool, page_table, step.slot_of_token, step.positions, out,
                        num_heads, num_kv_heads, head_dim, scale, window, value_dim=value_dim, sink=sink, gate=gate,
                        softcap=softcap, keep_first=keep_first)
@@ -1190,9 +1198,7 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
                          num_heads, num_kv_heads, head_dim, scale, window, num_splits=splits, plan=plan, sink=sink, gate=gate,
                          softcap=softcap, keep_first=keep_first)
         return
-    if not step.is_decode and attention_prefill_tc_supported(q.dtype, num_heads, num_kv_heads, head_dim) \
-            and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 \
-            and (gate is None or (gate.data_ptr() % 16 == 0 and gate.stride(0) % 8 == 0)):
+    if tc_prefill:
         order = None
         derived = getattr(step, "derived", None)
         if derived is not None and len(step.q_lens) > 1:     # one sequence: the kernel's own reverse order is the heaviest first
@@ -1201,7 +1207,7 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
                 order = derived["prefill_tile_order"] = prefill_tile_order(step.q_lens, step.kv_lens_host, q.device)
         attention_prefill_tc(q, k_pool, v_pool, page_table, step.cu_seqlens, step.seq_slots, step.kv_lens,
                              step.q_lens, out, num_heads, num_kv_heads, head_dim, scale, window, tile_order=order,
-                             sink=sink, gate=gate)
+                             sink=sink, gate=gate, softcap=softcap, keep_first=keep_first)
         return
     if not step.is_decode and attention_prefill_supported(q.dtype, num_heads, num_kv_heads, head_dim) \
             and (gate is None or (gate.data_ptr() % 4 == 0 and gate.stride(0) % 2 == 0)):

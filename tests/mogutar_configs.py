@@ -228,13 +228,13 @@ def random_config(seed):
                      softcap=rng.choice([None, 1.5, 10.0, 50.0]), window=window, keep_first=rng.choice([0, 1, 3, 7, 64, 70]), rot=r)
             sh = rng.choice([1, 2, 3, 4, 8])
             sg = rng.choice([g for g in range(1, sh + 1) if sh % g == 0])
-            sp = rng.choice([4, 8, 12, 32])
+            sp = rng.choice([8, 12, 16, 32])
             ng = rng.choice([g for g in (1, 2, 3, 4) if (sh * sp) % g == 0])
-            layers.append(parallel(l, right(sh, sp, rng.choice([4, 16, 20, 48, 64]), sg, rng.choice([1, 2, 3, 4]), ng),
+            layers.append(parallel(l, right(sh, sp, rng.choice([8, 16, 20, 48, 64]), sg, rng.choice([1, 2, 3, 4]), ng),
                                    rng.choice([0.5, 1.0, 1.2]), rng.choice([0.7, 1.0, 1.4]), some_mlp()))
         else:
             heads = rng.choice([1, 2, 3, 5])
-            layers.append(lightning(heads, rng.choice([8, 20, 32, 64, 72]), rng.choice([4, 16, 24, 40]),
+            layers.append(lightning(heads, rng.choice([8, 20, 32, 64, 72]), rng.choice([8, 16, 24, 40]),
                                     [rng.choice([0.3, 0.8, 0.95, 0.99, 0.9995]) for _ in range(heads)], some_mlp()))
     cfg = {"architecture": "Mogutar", "vocab": rng.choice([17, 64, 101, 300]), "width": width,
            "norm": {"eps": rng.choice([1e-6, 1e-5, 1e-3])}, "layers": layers}
