@@ -64,13 +64,15 @@ linear_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, in
   const float rate_h = rate[h], bias_h = mode ? dt_bias[h] : 0.f;
   const float neg_rate = mode ? -expf(rate_h) : 0.f;
 
-  // what a thread stages of a tile: NPT elements of q and of k (element idx = tid + j * THREADS of the tile's
+  // what a thread stages of a tile: QI elements of q and of k (element idx = tid + j * THREADS of the tile's
   // [SCAN_TILE, DKP]), one of v (threads below SCAN_TILE * SCAN_COLS) with its token's raw step size
   constexpr int VT = SCAN_TILE * SCAN_COLS;
-  float fq[LONG ? NPT : 1], fk[LONG ? NPT : 1], fv = 0.f, fdt = 0.f;
+  constexpr int QI = LONG ? SCAN_TILE * DKP / THREADS : 1;
+  static_assert(!LONG || QI * THREADS == SCAN_TILE * DKP, "a tile's q and k are dealt evenly to the threads");
+  float fq[QI], fk[QI], fv = 0.f, fdt = 0.f;
   auto fetch = [&](int t0, int nt) {            // raw values of the tile at t0 into registers (zeros outside)
 #pragma unroll
-    for (int j = 0; j < (LONG ? NPT : 1); ++j) {
+    for (int j = 0; j < QI; ++j) {
       const int idx = tid + j * THREADS, tt = idx / DKP, n = idx % DKP;
       const bool in = tt < nt && n < dk;
       fq[j] = in ? rl_ld(q + (size_t)(t0 + tt) * ldq + qk0 + n) : 0.f;
@@ -85,7 +87,7 @@ linear_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, in
   auto step_size = [&](float raw) { const float z = raw + bias_h; return z > 20.0f ? z : log1pf(expf(z)); };
   auto commit = [&]() {                         // the fetched values, activated, into shared memory
 #pragma unroll
-    for (int j = 0; j < (LONG ? NPT : 1); ++j) {
+    for (int j = 0; j < QI; ++j) {
       const int idx = tid + j * THREADS, tt = idx / DKP, n = idx % DKP;
       float qv = fq[j], kv = fk[j];
       if (act && n < dk) { qv = scan_silu(qv, T()); kv = scan_silu(kv, T()); }

@@ -229,7 +229,7 @@ def random_config(seed):
             sh = rng.choice([1, 2, 3, 4, 8])
             sg = rng.choice([g for g in range(1, sh + 1) if sh % g == 0])
             sp = rng.choice([8, 12, 16, 32])
-            ng = rng.choice([g for g in (1, 2, 3, 4) if (sh * sp) % g == 0])
+            ng = rng.choice([g for g in (1, 2, 3, 4) if (sh * sp) % g == 0 and (g == 1 or sh * sp // g >= 24)])   # a norm over a dozen values turns rounding into direction
             layers.append(parallel(l, right(sh, sp, rng.choice([8, 16, 20, 48, 64]), sg, rng.choice([1, 2, 3, 4]), ng),
                                    rng.choice([0.5, 1.0, 1.2]), rng.choice([0.7, 1.0, 1.4]), some_mlp()))
         else:
