@@ -25,10 +25,6 @@ __device__ __forceinline__ float nf_block_sum(float v, float* s_part) {
   return t;
 }
 
-// rows of up to NF_THREADS * NF_KEEP values stay in registers between the sum of squares and the update: one
-// trip to memory; longer rows are read twice
-#define NF_KEEP 16
-
 __global__ void __launch_bounds__(NF_THREADS)
 norm_add_kernel(float* __restrict__ x, const float* __restrict__ y0, float s0, const float* __restrict__ y1, float s1,
                 const float* __restrict__ w, float eps, int d, __nv_bfloat16* __restrict__ x_bf16) {
@@ -37,31 +33,6 @@ norm_add_kernel(float* __restrict__ x, const float* __restrict__ y0, float s0, c
   rl_pdl_wait();
   const size_t row = (size_t)blockIdx.x * d;
   float ss = 0.f;
-  if (d <= NF_THREADS * NF_KEEP) {
-    float v[NF_KEEP], xs[NF_KEEP];
-#pragma unroll
-    for (int j = 0; j < NF_KEEP; ++j) {
-      const int i = threadIdx.x + j * NF_THREADS;
-      v[j] = 0.f;
-      xs[j] = 0.f;
-      if (i < d) {
-        v[j] = y1 ? fmaf(s1, y1[row + i], s0 * y0[row + i]) : s0 * y0[row + i];
-        xs[j] = x[row + i];
-      }
-      ss = fmaf(v[j], v[j], ss);
-    }
-    const float r = 1.0f / sqrtf(nf_block_sum(ss, s_part) / (float)d + eps);
-#pragma unroll
-    for (int j = 0; j < NF_KEEP; ++j) {
-      const int i = threadIdx.x + j * NF_THREADS;
-      if (i < d) {
-        const float nx = xs[j] + v[j] * r * w[i];
-        x[row + i] = nx;
-        if (x_bf16) x_bf16[row + i] = __float2bfloat16_rn(nx);
-      }
-    }
-    return;
-  }
   for (int i = threadIdx.x; i < d; i += NF_THREADS) {
     const float v = y1 ? fmaf(s1, y1[row + i], s0 * y0[row + i]) : s0 * y0[row + i];
     ss = fmaf(v, v, ss);
@@ -91,27 +62,6 @@ gated_norm_kernel(const float* __restrict__ y, int ldy, const T* __restrict__ ga
   const float* yr = y + (size_t)m * ldy + c0;
   const T* gr = gate + (size_t)m * ldg + c0;
   float ss = 0.f;
-  if (n <= NF_THREADS * NF_KEEP) {                   // the group's values and gates stay in registers: one trip to memory
-    float v[NF_KEEP], g[NF_KEEP];
-#pragma unroll
-    for (int j = 0; j < NF_KEEP; ++j) {
-      const int i = threadIdx.x + j * NF_THREADS;
-      v[j] = 0.f;
-      g[j] = 0.f;
-      if (i < n) {
-        g[j] = nf_act(rl_ld(gr + i), act);
-        v[j] = gate_first ? yr[i] * g[j] : yr[i];
-      }
-      ss = fmaf(v[j], v[j], ss);
-    }
-    const float r = 1.0f / sqrtf(nf_block_sum(ss, s_part) / (float)n + eps);
-#pragma unroll
-    for (int j = 0; j < NF_KEEP; ++j) {
-      const int i = threadIdx.x + j * NF_THREADS;
-      if (i < n) rl_st(out + (size_t)m * ldo + c0 + i, gate_first ? v[j] * r * w[c0 + i] : v[j] * r * w[c0 + i] * g[j]);
-    }
-    return;
-  }
   for (int i = threadIdx.x; i < n; i += NF_THREADS) {
     const float v = gate_first ? yr[i] * nf_act(rl_ld(gr + i), act) : yr[i];
     ss = fmaf(v, v, ss);

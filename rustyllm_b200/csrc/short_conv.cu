@@ -21,10 +21,16 @@
 #define CONV_MAX_TAPS 8
 #define CONV_THREADS 256
 
+// how many of rows m - 1, m - 2, ... (at most taps - 1) belong to row m's sequence.  The slots are loaded
+// independently of one another (no load waits for the one before it), then counted while the run lasts.
 __device__ __forceinline__ int conv_rows_back(const int* __restrict__ slot_of_token, int m, int taps) {
   const int slot = slot_of_token[m];
-  int n = 0;
-  while (n < taps - 1 && m - n - 1 >= 0 && slot_of_token[m - n - 1] == slot) ++n;
+  int same[CONV_MAX_TAPS - 1];
+#pragma unroll
+  for (int d = 1; d < CONV_MAX_TAPS; ++d) same[d - 1] = (d < taps && m - d >= 0) ? (slot_of_token[m - d] == slot) : 0;
+  int n = 0, run = 1;
+#pragma unroll
+  for (int d = 1; d < CONV_MAX_TAPS; ++d) { run &= same[d - 1]; n += run; }
   return n;
 }
 
