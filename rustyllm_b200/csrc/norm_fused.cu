@@ -74,6 +74,34 @@ gated_norm_kernel(const float* __restrict__ y, int ldy, const T* __restrict__ ga
   }
 }
 
+// The same for groups of up to 1,024 values in steps of many tokens: a warp a (token, group), eight a block, no
+// barrier; the second pass finds the group in L1.
+template <typename T>
+__global__ void __launch_bounds__(NF_THREADS)
+gated_norm_warp_kernel(const float* __restrict__ y, int ldy, const T* __restrict__ gate, int ldg, int act, int gate_first,
+                       const float* __restrict__ w, float eps, int n, int groups, long long rows, T* __restrict__ out, int ldo) {
+  rl_pdl_trigger();
+  rl_pdl_wait();
+  const long long row = (long long)blockIdx.x * (NF_THREADS / 32) + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  const long long m = row / groups;
+  const int c0 = (int)(row % groups) * n;
+  const float* yr = y + (size_t)m * ldy + c0;
+  const T* gr = gate + (size_t)m * ldg + c0;
+  float ss = 0.f;
+  for (int i = lane; i < n; i += 32) {
+    const float v = gate_first ? yr[i] * nf_act(rl_ld(gr + i), act) : yr[i];
+    ss = fmaf(v, v, ss);
+  }
+  const float r = 1.0f / sqrtf(rl_warp_sum(ss) / (float)n + eps);
+  for (int i = lane; i < n; i += 32) {
+    const float g = nf_act(rl_ld(gr + i), act);
+    const float v = gate_first ? yr[i] * g * r * w[c0 + i] : yr[i] * r * w[c0 + i] * g;
+    rl_st(out + (size_t)m * ldo + c0 + i, v);
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(NF_THREADS)
 gelu_gate_kernel(const T* __restrict__ t, int ldt, const int* __restrict__ tokens, const T* __restrict__ table, int ld_table,
@@ -106,6 +134,20 @@ extern "C" int rl_gated_norm(const float* y, int ldy, const void* gate, int ldg,
   RL_REQUIRE((act == 0 || act == 1) && (gate_first == 0 || gate_first == 1), "rl_gated_norm: unknown option");
   if (num_tokens == 0) return RL_OK;
   const dim3 grid(num_tokens, groups);
+  const long long rows = (long long)num_tokens * groups;
+  if (n <= 1024 && rows >= 4096) {          // many small groups: a warp each
+    const unsigned blocks = (unsigned)((rows + NF_THREADS / 32 - 1) / (NF_THREADS / 32));
+    if (dtype == RL_F32)
+      rl_launch_pdl(gated_norm_warp_kernel<float>, blocks, NF_THREADS, 0, stream, y, ldy, (const float*)gate, ldg, act, gate_first, weight,
+                    eps, n, groups, rows, (float*)out, ldo);
+    else if (dtype == RL_BF16)
+      rl_launch_pdl(gated_norm_warp_kernel<__nv_bfloat16>, blocks, NF_THREADS, 0, stream, y, ldy, (const __nv_bfloat16*)gate, ldg, act,
+                    gate_first, weight, eps, n, groups, rows, (__nv_bfloat16*)out, ldo);
+    else
+      RL_REQUIRE(false, "rl_gated_norm: unknown dtype %d", dtype);
+    RL_LAUNCH_CHECK("rl_gated_norm");
+    return RL_OK;
+  }
   if (dtype == RL_F32)
     rl_launch_pdl(gated_norm_kernel<float>, grid, NF_THREADS, 0, stream, y, ldy, (const float*)gate, ldg, act, gate_first, weight, eps,
                   n, (float*)out, ldo);

@@ -109,12 +109,12 @@ def state_area(slots, nbytes, pad=256):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("taps,portions", [(4, [(5, 1, 1, 2, 30), (1, 1, 1, 1, 7)]), (2, [(3, 9), (12,)]), (1, [(4, 4), (8,)]),
                                            (8, [(2, 2, 2, 20), (26,)])])
-def test_short_convolution_across_steps(dtype, taps, portions):
+@pytest.mark.parametrize("Cn,lead,pad", [(37, 5, 11), (40, 8, 16)])      # odd channels in a misaligned view; eights, 16-byte aligned
+def test_short_convolution_across_steps(dtype, taps, portions, Cn, lead, pad):
     """Two sequences packed in every step, cut differently, against the whole-sequence convolution; the state
     carries the last taps - 1 inputs, also through portions shorter than the filter."""
     from rustyllm_b200 import kernels as K
     torch.manual_seed(taps)
-    Cn = 37
     n = [sum(p) for p in portions]
     assert len(set(len(p) for p in portions)) <= 2
     u = [rounded(torch.randn(t, Cn, dtype=F64), dtype) for t in n]
@@ -128,9 +128,9 @@ def test_short_convolution_across_steps(dtype, taps, portions):
         live = [s for s in range(2) if step < len(portions[s])]
         cnt = [portions[s][step] for s in live]
         rows = torch.cat([u[s][at[s]:at[s] + c] for s, c in zip(live, cnt)])
-        wide = torch.zeros((rows.shape[0], Cn + 11), dtype=tdt(dtype), device=DEV)       # a view with a wider row stride
-        wide[:, 5:5 + Cn] = rows.to(tdt(dtype)).to(DEV)
-        uin = wide[:, 5:5 + Cn]
+        wide = torch.zeros((rows.shape[0], Cn + pad), dtype=tdt(dtype), device=DEV)       # a view with a wider row stride
+        wide[:, lead:lead + Cn] = rows.to(tdt(dtype)).to(DEV)
+        uin = wide[:, lead:lead + Cn]
         out = torch.empty((rows.shape[0], Cn), dtype=tdt(dtype), device=DEV)
         slot_of_token = i32([slots[s] for s, c in zip(live, cnt) for _ in range(c)])
         cu = i32([0] + list(np.cumsum(cnt)))
@@ -234,6 +234,15 @@ def test_norms_on_a_sublayers_output(dtype):
     K.gated_norm(y.to(DEV), gate.to(tdt(dtype)).to(DEV), wn.to(DEV), eps, out, groups=1, gate_act="sigmoid", gate_first=False)
     ref = P.rms_norm(y.double(), wn.double(), eps) * P.sigmoid(gate)
     torch.testing.assert_close(out.double().cpu(), ref, **tol(dtype))
+    # many small groups (a warp a group)
+    M2, n2, g2 = 600, 96, 8
+    y2 = torch.randn(M2, n2, dtype=F64).float()
+    gate2 = rounded(torch.randn(M2, n2, dtype=F64), dtype)
+    w2 = (1 + 0.1 * torch.randn(n2, dtype=F64)).float()
+    out2 = torch.empty((M2, n2), dtype=tdt(dtype), device=DEV)
+    K.gated_norm(y2.to(DEV), gate2.to(tdt(dtype)).to(DEV), w2.to(DEV), eps, out2, groups=g2, gate_act="silu", gate_first=True)
+    ref2 = P.rms_norm((y2.double() * P.silu(gate2)).view(M2, g2, n2 // g2), None, eps).reshape(M2, n2) * w2.double()
+    torch.testing.assert_close(out2.double().cpu(), ref2, **tol(dtype))
     # the token's learned vector times gelu of a projection
     V, cols, col0, width = 11, 30, 12, 6
     t = rounded(torch.randn(M, width, dtype=F64), dtype)
