@@ -9,7 +9,7 @@ uses together with the shared one are as wide as the dense feed-forward), vocabu
                  heads x head size rows), dense feed-forward, soft-capped logits
   mosurax-moe    the same with every second layer's feed-forward a mixture of experts with a shared expert
   mogutar        post-norm layers, two in four with attention (convolved, normed, rotated q and k; soft-capped scores; a
-                 window of 1,024 with 4 kept tokens) beside a selective state-space mixer of the model's width, two in
+                 window of 1,024 with 8 kept tokens) beside a selective state-space mixer of the model's width, two in
                  four with linear attention with decay; every feed-forward 16 experts in 4 groups (2 kept), 4 a token,
                  each a quarter of the dense width; a per-layer token input of 256 columns
 ``--kernels`` times the Mogutar design's own kernels alone at the sizes of a layer (a JSON line a kernel, with the
@@ -57,8 +57,8 @@ def mosurax_config(s: dict, experts: bool, window=None) -> dict:
 
 def mogutar_config(s: dict, window: int = 1024) -> dict:
     left = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"], "scale": s["dim"] ** -0.5, "conv": 4,
-            "softcap": 50.0, "mask": {"size": window, "keep_first": 4},
-            "rot": {"base": 500000.0, "dims": s["dim"] // 2, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+            "softcap": 30.0, "mask": {"size": window, "keep_first": 8},
+            "rot": {"base": 1.0e6, "dims": s["dim"] // 2, "scaling": {"factor": 8.0, "original": 8192, "fast": 16.0, "slow": 2.0}}}
     right = {"heads": s["width"] // 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8}
     mlp = {"kind": "moe", "router": {"experts": s["experts"], "top": 4, "groups": {"count": 4, "keep": 2}}, "expert": {"ff": s["expert_ff"]}}
     layers = []

@@ -85,11 +85,11 @@ CONFIGS = {
     # borders and none, no token input, four taps, experts with all groups kept and with top = all
     "U": {"architecture": "Mogutar", "vocab": 211, "width": 128, "norm": {"eps": 1e-6},
           "layers": [parallel(left(4, 1, 64, 64, 0.125, conv=4, softcap=30.0, window=130, keep_first=3, rot=rot(16, 1.0e6, (8.0, 128, 16.0, 2.0))),
-                              right(2, 32, 24, 2, 4, 4), 1.0, 1.0, moe(8, 2, 32, groups=(4, 4))),
+                              right(2, 32, 24, 2, 4, 2), 1.0, 1.0, moe(8, 2, 32, groups=(4, 4))),
                      lightning(4, 32, 16, [0.6, 0.9, 0.99, 0.999], moe(3, 3, 24)),
                      parallel(left(2, 1, 64, 64, 0.11, conv=4, window=None, rot=rot(64, 10000.0)),
-                              right(8, 8, 32, 4, 3, 1), 1.2, 0.9, None),
-                     parallel(left(4, 2, 64, 64, 0.125, conv=4, softcap=8.0, window=65, keep_first=0, rot=rot(32, 50000.0, (4.0, 256, 32.0, 1.0))),
+                              right(8, 8, 32, 4, 3, 1), 1.1, 0.8, None),
+                     parallel(left(4, 2, 64, 64, 0.125, conv=4, softcap=8.0, window=65, keep_first=0, rot=rot(32, 50000.0, (4.0, 256, 24.0, 1.0))),
                               right(2, 32, 24, 1, 4, 2), 0.5, 1.5, moe(6, 3, 16, groups=(2, 1)))]},
     # a width that is no multiple of 64, an odd vocabulary, value heads narrower than key heads, one tap (a gain a
     # channel) and no convolution, no rotation, a window of 1 and of 2, lightning layers first
@@ -222,10 +222,10 @@ def random_config(seed):
             r = None
             if rng.random() < 0.8:
                 dims = rng.choice([x for x in (2, 4, 8, 16, dim) if x <= dim and x % 2 == 0])
-                r = rot(dims, rng.choice([100.0, 10000.0, 500000.0]),
-                        rng.choice([None, (2.0, 64, 8.0, 1.0), (4.0, 512, 32.0, 1.0), (16.0, 100, 4.0, 0.5)]))
+                r = rot(dims, rng.choice([100.0, 10000.0, 200000.0]),
+                        rng.choice([None, (2.0, 64, 8.0, 1.0), (4.0, 512, 24.0, 1.0), (16.0, 100, 4.0, 0.5)]))
             l = left(heads, kv, dim, vdim, rng.choice([0.05, 0.125, 0.3, 1.0 / math.sqrt(dim)]), conv=rng.choice([0, 1, 2, 3, 4]),
-                     softcap=rng.choice([None, 1.5, 10.0, 50.0]), window=window, keep_first=rng.choice([0, 1, 3, 7, 64, 70]), rot=r)
+                     softcap=rng.choice([None, 1.5, 10.0, 40.0]), window=window, keep_first=rng.choice([0, 1, 3, 7, 64, 70]), rot=r)
             sh = rng.choice([1, 2, 3, 4, 8])
             sg = rng.choice([g for g in range(1, sh + 1) if sh % g == 0])
             sp = rng.choice([8, 12, 16, 32])

@@ -63,7 +63,7 @@ def test_configuration_errors_name_the_key():
 
 
 def test_stretched_frequencies_follow_the_plain_statement():
-    for dims, base, sc in ((8, 10000.0, (2.0, 64, 8.0, 1.0)), (64, 1.0e6, (8.0, 4096, 32.0, 1.0)), (32, 500000.0, (4.0, 1024, 32.0, 1.0)),
+    for dims, base, sc in ((8, 10000.0, (2.0, 64, 8.0, 1.0)), (64, 1.0e6, (8.0, 4096, 32.0, 1.0)), (32, 300000.0, (4.0, 2048, 24.0, 1.0)),
                            (4, 100.0, (16.0, 100, 4.0, 0.5))):
         want, mult = P.yarn_frequencies(dims, base, dict(zip(("factor", "original", "fast", "slow"), sc)))
         got = yarn_inverse_frequencies(base, dims, *sc)
