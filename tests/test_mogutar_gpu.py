@@ -313,7 +313,7 @@ def _masked_attention(dtype, H, G, hd, vd, window, keep_first, scale, cap, q, k,
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("H,G,hd,vd", [(4, 2, 16, 24), (2, 1, 64, 64), (2, 2, 128, 128)])
-@pytest.mark.parametrize("window,keep_first", [(9, 2), (70, 5), (64, 64), (130, 3), (1, 1), (None, 0), (40, 0)])
+@pytest.mark.parametrize("window,keep_first", [(9, 2), (70, 5), (64, 64), (130, 3), (1, 1), (None, 0), (40, 0), (100, 150)])
 def test_one_key_stands_out_at_the_edges_of_window_and_kept_tokens(dtype, H, G, hd, vd, window, keep_first):
     """Scores are flat but for one key that a query meets with a score 12 above the rest: its value must dominate
     the output exactly while the key is inside the window or among the kept first tokens, and vanish the token
