@@ -281,11 +281,28 @@ def run_kernel_benchmark(runner, runs: int, as_json: bool, layer_index: int = 0)
     xn = torch.empty(1, d, device=dev, dtype=dt)
     rows = []
     rows.append(("attn_norm.rms", timed(lambda: K.rmsnorm(x, blk.mixer_norm.weight, xn, blk.mixer_norm.eps)), d * 4))
-    qkv = torch.empty(1, att.wqkv.shape[0], device=dev, dtype=att.wqkv.dtype)
-    xq = xn.to(att.wqkv.dtype)
-    rows.append(("attn_qkv.fused", timed(lambda: linear(xq, att.wqkv, qkv, OUT_SAME, att.bqkv)), att.wqkv.numel() * att.wqkv.element_size()))
-    a = torch.randn(1, att.wo.shape[1], device=dev).to(att.wo.dtype)
-    rows.append(("attn_output", timed(lambda: linear(a, att.wo, x, OUT_ADD_F32, att.bo)), att.wo.numel() * att.wo.element_size()))
+
+    def product_rows(tag, w_in, b_in, w_out, b_out):
+        """The input and output products of a mixer."""
+        y = torch.empty(1, w_in.shape[0], device=dev, dtype=w_in.dtype)
+        xq = xn.to(w_in.dtype)
+        rows.append((f"{tag}.fused", timed(lambda: linear(xq, w_in, y, OUT_SAME, b_in)), w_in.numel() * w_in.element_size()))
+        a = torch.randn(1, w_out.shape[1], device=dev).to(w_out.dtype)
+        rows.append((f"{tag.split('_')[0]}_output", timed(lambda: linear(a, w_out, x, OUT_ADD_F32, b_out)), w_out.numel() * w_out.element_size()))
+        return y
+
+    # mixers side by side: the attention's rows under "attn", the other mixer's products under "mixer2"; a mixer
+    # without keys and values (a recurrence): its two products alone
+    other = None
+    if hasattr(att, "left") and hasattr(att, "right"):
+        att, other = (att.left, att.right) if hasattr(att.left, "wqkv") else (att.right, att.left)
+    qkv = None
+    if hasattr(att, "wqkv"):
+        qkv = product_rows("attn_qkv", att.wqkv, att.bqkv, att.wo, att.bo)
+    for m, tag in ((other, "mixer2_in"), (None if hasattr(att, "wqkv") else att, "mixer_in")):
+        w_in = next((getattr(m, n) for n in ("w_in", "wqkvg") if m is not None and getattr(m, n, None) is not None), None)
+        if w_in is not None:
+            product_rows(tag, w_in, None, m.wo, None)
     from .parts.mlp import GatedMLP
     from .parts.moe import MoEMLP
 
@@ -303,7 +320,11 @@ def run_kernel_benchmark(runner, runs: int, as_json: bool, layer_index: int = 0)
         xe = xn.to(ff.router.dtype)
         ids = torch.empty((1, ff.top), dtype=torch.int32, device=dev)
         wts = torch.empty((1, ff.top), dtype=torch.float32, device=dev)
-        rows.append(("ffn_router", timed(lambda: K.moe_route(xe, ff.router, ff.router_b, ff.top, ids, wts)), ff.router.numel() * esz))
+        if getattr(ff, "scoring", "softmax") == "sigmoid":
+            rows.append(("ffn_router", timed(lambda: K.moe_route_sigmoid(xe, ff.router, ff.correction, ff.top, ff.groups, ff.keep_groups, ids, wts)),
+                         ff.router.numel() * esz))
+        else:
+            rows.append(("ffn_router", timed(lambda: K.moe_route(xe, ff.router, ff.router_b, ff.top, ids, wts)), ff.router.numel() * esz))
         shared, ff.shared = ff.shared, None
         try:
             rows.append(("ffn_experts.chosen", timed(lambda: ff.forward(xe, x, None)), ff.router.numel() * esz + ff.top * 3 * ff.F * ff.d * esz))
@@ -319,7 +340,7 @@ def run_kernel_benchmark(runner, runs: int, as_json: bool, layer_index: int = 0)
     eng = runner.engine
     max_ctx = min(runner.cache.max_seq_len, runner.cache.free_pages * runner.cache.page_size)
     for ctx in (32, 128, 512, 2048, 8192):
-        if ctx + 1 > max_ctx:
+        if ctx + 1 > max_ctx or qkv is None:
             break
         s = eng.alloc_slot()
         eng.step([s], [[1] * ctx], None)
@@ -328,12 +349,13 @@ def run_kernel_benchmark(runner, runs: int, as_json: bool, layer_index: int = 0)
         group, layer = runner.cache.kv_entry(entry)
         st = eng.step_state(torch.tensor([1, ctx, s, 0, 1, s, ctx + 1, 0], dtype=torch.int32, device=dev), (1, 1, 1), [1], [ctx + 1])
         runner.cache.prepare([s], [1])
-        q = torch.randn(1, qkv.shape[1], device=dev).to(dt)
+        q = torch.randn(1, max(qkv.shape[1], 8), device=dev).to(dt)
         o = torch.empty(1, att.H * att.vd, device=dev, dtype=dt)
         n_qkv = (att.H + att.G) * att.hd + att.G * att.vd
         gate = q[:, n_qkv:] if getattr(att, "gated", False) else None
         t = timed(lambda: K.attention(q, group.k_pool(layer), group.v_pool(layer), group.page_table, st, o, att.H, att.G, att.hd, att.scale,
-                                      att.window or 0, value_dim=att.vd, sink=getattr(att, "sink", False), gate=gate))
+                                      att.window or 0, value_dim=att.vd, sink=getattr(att, "sink", False), gate=gate,
+                                      softcap=getattr(att, "softcap", 0.0), keep_first=getattr(att, "keep_first", 0)))
         seen = min(ctx + 1, att.window) if att.window else ctx + 1
         rows.append((f"attn_scan.ctx{ctx}", t, seen * att.G * (att.hd + att.vd) * esz))
         eng.free_slot(s)
