@@ -11,7 +11,7 @@
 //
 // A block owns 8 or 16 columns of one head's state of one sequence and walks the sequence's tokens of
 // the step in order; R neighbouring lanes share a column (each holds NPT consecutive rows) and add their
-// parts of q . S[:, col] by shuffles.  Tokens are staged SCAN_TILE at a time in shared memory.  The walk is
+// parts of q . S[:, col] by shuffles.  Tokens are staged 16 (8 in the shape for single-token steps) at a time in shared memory.  The walk is
 // one dependent multiply-add a state element and token; everything else (the loads of q and k from shared
 // memory, the dot product, the shuffles) is latency to hide, so R grows with dk (8, 16, 32: a block of 128,
 // 256 or 512 threads, at most 8 state elements a thread): more warps an SM, fewer instructions a thread.
@@ -21,7 +21,6 @@
 
 #include "common.cuh"
 
-#define SCAN_TILE 16
 #define SCAN_MAX_DK 256
 
 // silu at the load: accurate in a 32-bit run; with the fast exponential and division in a bfloat16 run, whose
@@ -29,7 +28,7 @@
 __device__ __forceinline__ float scan_silu(float z, float) { return z / (1.0f + expf(-z)); }
 __device__ __forceinline__ float scan_silu(float z, __nv_bfloat16) { return __fdividef(z, 1.0f + __expf(-z)); }
 
-template <typename T, int NPT, int R, int SCAN_COLS>
+template <typename T, int NPT, int R, int SCAN_COLS, int SCAN_TILE>
 __global__ void __launch_bounds__(R * SCAN_COLS)
 linear_scan_kernel(const T* __restrict__ q, int ldq, const T* __restrict__ k, int ldk, const T* __restrict__ v, int ldv,
                    const T* __restrict__ dt_raw, int lddt, const float* __restrict__ dt_bias, const float* __restrict__ rate,
@@ -189,9 +188,11 @@ static int scan_launch(const void* q, int ldq, const void* k, int ldk, const voi
                        const int* seq_slots, int num_seqs, float* state, long long state_stride, float* out, int ldo, int H,
                        int hpg, int dk, int dv, int wide, cudaStream_t stream) {
 #define SCAN_GO(NPT, R, COLS)                                                                                                      \
-  rl_launch_pdl(linear_scan_kernel<T, NPT, R, COLS>, dim3(num_seqs, H, (dv + COLS - 1) / COLS), R * COLS, 0, stream, (const T*)q, ldq, \
+  rl_launch_pdl(linear_scan_kernel<T, NPT, R, COLS, (NPT > 8 ? 8 : 16)>, dim3(num_seqs, H, (dv + COLS - 1) / COLS), R * COLS, 0, stream, (const T*)q, ldq, \
                 (const T*)k, ldk, (const T*)v, ldv, (const T*)dt_raw, lddt, dt_bias, rate, skip, mode, act, cu_seqlens, seq_slots,      \
                 state, state_stride, out, ldo, H, hpg, dk, dv)
+  // tokens a tile: 8 in the shape for single-token steps (64 registers a thread and half the shared memory: 35.7
+  // against 39.7 us at 64 sequences), 16 in long steps (8: 759 against 575 us, a barrier pair every 8 tokens)
   // columns of the state a block: 16 in single-token steps (fewer, larger blocks: 0.52 against 0.43 of the copy
   // bandwidth at 64 sequences), 8 in long steps (two blocks an SM whose phases overlap: 575 against 655 us for
   // 2,048 tokens of 16 heads of 128 x 128)
