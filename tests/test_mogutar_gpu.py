@@ -413,6 +413,23 @@ def test_prompt_then_token_by_token_equals_whole(dirs, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_long_prompt_then_decoding(dirs, dtype):
+    """900 tokens in one step (seven 128-key tiles, fourteen pages, the windows far from the kept first tokens), then
+    24 single tokens; head size 64: the tensor-core attention kernels in the bfloat16 run."""
+    d = dirs["U", dtype]
+    cfg, _ = _plain(d)
+    r = runner(d, dtype)
+    toks = random_tokens(cfg["vocab"], 924, 91)
+    ref = plain_logits(d, toks)
+    s = r.engine.alloc_slot()
+    rows = [r.engine.step([s], [toks[:900]], [list(range(0, 900, 7))])]
+    for t in range(900, 924):
+        rows.append(r.engine.step([s], [[toks[t]]], "last"))
+    r.engine.free_slot(s)
+    close(torch.cat(rows), ref[list(range(0, 900, 7)) + list(range(900, 924))], dtype, cfg, "U long")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("name", NAMES)
 @pytest.mark.parametrize("size", [2, 3, 7, 64, 100])
 def test_prompt_in_portions(dirs, name, dtype, size):
