@@ -156,6 +156,8 @@ class DecoderModel:
         for pos, li in enumerate(schedule):
             for part, args in self.injections.get(pos, ()):
                 part.forward(x, embedded, step, **args)
+                # a block may have left a rounded copy of the stream for the next reader: the stream has changed
+                getattr(step, "derived", {}).pop(("stream_rounded", id(x)), None)
             entry, writes = self.run_entry[pos]
             where = cache.entry_group[entry]
             view = CacheView(

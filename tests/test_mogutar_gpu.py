@@ -560,7 +560,7 @@ def test_trace_replay_and_command_line(dirs, tmp_path):
     for layer in ("0", "1"):          # a layer of mixers side by side, and one of linear attention
         p = subprocess.run([sys.executable, os.path.join(root, "bin", "rustyllm"), d, "--kernel-bench", "--kernel-bench-runs", "2",
                             "--kernel-bench-layer", layer], capture_output=True, text=True, timeout=600)
-        assert p.returncode == 0 and "ffn_experts.chosen" in p.stdout or "output" in p.stdout, p.stderr[-2000:]
+        assert p.returncode == 0 and "ffn_experts.chosen" in p.stdout and "output" in p.stdout, p.stderr[-2000:]
     p = subprocess.run([sys.executable, os.path.join(root, "bin", "rustyllm"), d, "--prompt", "1 2 3", "--max-tokens", "5", "--temp", "0"],
                        capture_output=True, text=True, timeout=600)
     assert p.returncode == 0, p.stderr[-2000:]
