@@ -557,10 +557,10 @@ def test_trace_replay_and_command_line(dirs, tmp_path):
         close(torch.cat([got0, got2]), ref[[0, 79, 89]], dtype, cfg, f"trace {dtype}")
     p = subprocess.run([sys.executable, os.path.join(root, "bin", "rustyllm"), d, "--inspect"], capture_output=True, text=True, timeout=600)
     assert p.returncode == 0 and "Mogutar" in p.stdout, p.stderr[-2000:]
-    for layer in ("0", "1"):          # a layer of mixers side by side, and one of linear attention
+    for layer, row in (("0", "attn_qkv.fused"), ("1", "mixer_in.fused")):      # mixers side by side; linear attention
         p = subprocess.run([sys.executable, os.path.join(root, "bin", "rustyllm"), d, "--kernel-bench", "--kernel-bench-runs", "2",
                             "--kernel-bench-layer", layer], capture_output=True, text=True, timeout=600)
-        assert p.returncode == 0 and "ffn_experts.chosen" in p.stdout and "output" in p.stdout, p.stderr[-2000:]
+        assert p.returncode == 0 and row in p.stdout and "output" in p.stdout, p.stderr[-2000:]
     p = subprocess.run([sys.executable, os.path.join(root, "bin", "rustyllm"), d, "--prompt", "1 2 3", "--max-tokens", "5", "--temp", "0"],
                        capture_output=True, text=True, timeout=600)
     assert p.returncode == 0, p.stderr[-2000:]
