@@ -227,6 +227,23 @@ def kernel_times(sizes: List[str], prompt: int = 2048, batch: int = 64, runs: in
             out = torch.empty((M, C), dtype=bf, device=dev)
             us = timed(lambda: (K.short_conv(xbc, w, None, True, slot_of_token, cstate, out), K.short_conv_state(xbc, 4, cu, slots, cstate)))
             report(name, "short_conv + state", f"{what}: {M} tokens, {C} channels, 4 taps", us, 2 * xbc.numel() * 2 + 2 * cstate.numel())
+            # the attention's preparation: convolution, head norms, rotation, cache write (keys and values to pages)
+            G = s["kv_heads"]
+            Cq = (H + 2 * G) * hd
+            pstate = torch.zeros((B, 4 * 3 * Cq), dtype=torch.uint8, device=dev)
+            u = torch.randn((M, Cq), dtype=torch.float32, device=dev).to(bf)
+            qo = torch.empty((M, H * hd), dtype=bf, device=dev)
+            pages = -(-per // K.PAGE_SIZE)
+            k_pool = torch.zeros((B * pages, G, K.PAGE_SIZE, hd), dtype=bf, device=dev)
+            v_pool = torch.zeros_like(k_pool)
+            table = torch.arange(B * pages, dtype=torch.int32, device=dev).view(B, pages)
+            positions = i32([t for b in range(B) for t in range(per)])
+            wq = torch.randn((Cq, 4), dtype=torch.float32, device=dev)
+            nw = torch.ones(hd, dtype=torch.float32, device=dev)
+            inv = torch.rand(hd // 4, dtype=torch.float32, device=dev)
+            us = timed(lambda: (K.qkv_prepare(u, qo, wq, pstate, nw, nw, 1e-5, positions, slot_of_token, table, inv, hd // 2, 1.1, H, G, hd, hd,
+                                              k_pool, v_pool), K.short_conv_state(u, 4, cu, slots, pstate)))
+            report(name, "qkv_prepare + state", f"{what}: {M} tokens, {H} + 2 x {G} heads of {hd}, 4 taps", us, 2 * u.numel() * 2 + 2 * pstate.numel())
             # gate, norm in groups
             yn = torch.empty((M, Hs * P), dtype=bf, device=dev)
             gate = torch.randn((M, Hs * P), dtype=torch.float32, device=dev).to(bf)
